@@ -1,2 +1,3 @@
 """Architectures this package knows; importing registers them."""
 from . import llama  # noqa: F401
+from . import fobilorn  # noqa: F401

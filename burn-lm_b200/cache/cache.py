@@ -32,25 +32,37 @@ class CacheView:
     """What one run of the schedule sees of the cache."""
     kind: str                               # "kv", "state" or "none"
     writes: bool                            # False: the line belongs to an earlier run; read only
-    pool: Optional[torch.Tensor] = None     # kv: [pages, 2, n_kv_heads, PAGE, head_dim]
+    pool: Optional[torch.Tensor] = None     # kv: [pages, 2, n_kv_heads, PAGE, head_dim]; with values of another size than
+                                            # the keys [pages, n_kv_heads * PAGE * (head_dim + value_dim)], a page's keys
+                                            # [n_kv_heads, PAGE, head_dim] followed by its values [n_kv_heads, PAGE, value_dim];
+                                            # ids: int32 [pages, PAGE]
     block_table: Optional[torch.Tensor] = None   # kv: int32 [max_seqs, max_pages_per_seq]
     state: Optional[torch.Tensor] = None    # state: [max_seqs, *state_shape]
     window: Optional[int] = None
+    keep_first: int = 0
 
 
 class _KVGroup:
     def __init__(self, need, runs, n_pages, max_seqs, max_pages_per_seq, dtype, device):
         self.need, self.runs = need, list(runs)
-        self.pool = torch.empty((len(runs), n_pages, 2, need.n_kv_heads, PAGE, need.head_dim), dtype=dtype, device=device)
+        if need.kind == "ids":
+            self.pool = torch.zeros((len(runs), n_pages, PAGE), dtype=torch.int32, device=device)
+        elif need.value_dim is None or need.value_dim == need.head_dim:
+            self.pool = torch.empty((len(runs), n_pages, 2, need.n_kv_heads, PAGE, need.head_dim), dtype=dtype, device=device)
+        else:
+            self.pool = torch.empty((len(runs), n_pages, need.n_kv_heads * PAGE * (need.head_dim + need.value_dim)),
+                                    dtype=dtype, device=device)
+        # leading pages that hold some of the first `keep_first` positions: a windowed group never gives them back
+        self.kept_pages = (need.keep_first + PAGE - 1) // PAGE if need.window else 0
         self.pages = IdAllocator(n_pages, "cache page")
         self.block_table = torch.zeros((max_seqs, max_pages_per_seq), dtype=torch.int32, device=device)
         # pages_of[slot][i]: the page that holds positions 64 i .. 64 i + 63 of the slot's sequence, or None once a
-        # windowed group has given it back; dropped[slot]: how many leading pages that is
+        # windowed group has given it back; dropped[slot]: the pages kept_pages .. dropped - 1 have been given back
         self.pages_of: list[list] = [[] for _ in range(max_seqs)]
         self.dropped = [0] * max_seqs
 
     def live_pages(self, slot: int) -> list:
-        return self.pages_of[slot][self.dropped[slot]:]
+        return [p for p in self.pages_of[slot] if p is not None]
 
     def drop_before_window(self, slot: int, length: int) -> None:
         """`length`: how long the slot's sequence is now; the tokens still to come sit at positions >= length and see
@@ -59,12 +71,13 @@ class _KVGroup:
             return
         first_needed = max(0, length - self.need.window + 1) // PAGE
         last = min(first_needed, len(self.pages_of[slot]))
-        if last > self.dropped[slot]:
-            for i in range(self.dropped[slot], last):
+        start = max(self.dropped[slot], self.kept_pages)
+        if last > start:
+            for i in range(start, last):
                 self.pages.release(self.pages_of[slot][i])
                 self.pages_of[slot][i] = None
             # the table's entries stay valid page numbers: no kernel reads them, but none may point outside the pool
-            self.block_table[slot, self.dropped[slot]:last] = 0
+            self.block_table[slot, start:last] = 0
             self.dropped[slot] = last
 
     def bytes(self):
@@ -79,8 +92,9 @@ class _StateGroup:
 
 
 class Cache:
-    def __init__(self, needs: list, schedule, max_tokens: int, max_seqs: int, max_seq_len: int, dtype, device):
-        """needs[run]: CacheNeed of every run of the schedule (None where the run reads another's)."""
+    def __init__(self, needs: list, schedule, max_tokens: int, max_seqs: int, max_seq_len: int, dtype, device, named=None):
+        """needs[run]: CacheNeed of every run of the schedule (None where the run reads another's).  `named`: what parts
+        outside the layers keep per sequence (the embedding, say), name -> CacheNeed; their views are `named_view(name)`."""
         if max_tokens < 1 or max_seqs < 1 or max_seq_len < 1:
             raise CacheError("the cache needs room for at least one token of one sequence")
         self.max_tokens, self.max_seqs, self.max_seq_len = max_tokens, max_seqs, max_seq_len
@@ -96,8 +110,10 @@ class Cache:
         for run, need in enumerate(needs):
             if need is not None:
                 by_need.setdefault(need, []).append(run)
+        for name, need in (named or {}).items():
+            by_need.setdefault(need, []).append(("named", name))
         for need, runs in by_need.items():
-            if need.kind == "kv":
+            if need.kind in ("kv", "ids"):
                 # (a windowed group has storage of its own; the window is applied in the kernels, and the
                 # group gives the pages before it back as the sequence grows)
                 g = _KVGroup(need, runs, self.n_pages, max_seqs, self.max_pages_per_seq, dtype, device)
@@ -119,16 +135,24 @@ class Cache:
             src = run if entry.cache_of is None else entry.cache_of
             kind, g, i = self._where[src]
             writes = entry.cache_of is None
-            if kind == "kv":
-                self._views.append(CacheView("kv", writes, pool=g.pool[i], block_table=g.block_table, window=g.need.window))
-            elif kind == "state":
-                self._views.append(CacheView("state", writes, state=g.state[i]))
-            else:
-                self._views.append(CacheView("none", writes))
+            self._views.append(self._view_of(kind, g, i, writes))
+        self._named_views = {name: self._view_of(*self._where[("named", name)], True) for name in (named or {})}
+
+    @staticmethod
+    def _view_of(kind, g, i, writes):
+        if kind == "kv":
+            return CacheView(g.need.kind, writes, pool=g.pool[i], block_table=g.block_table, window=g.need.window,
+                             keep_first=g.need.keep_first)
+        if kind == "state":
+            return CacheView("state", writes, state=g.state[i])
+        return CacheView("none", writes)
 
     # -- what the model sees -------------------------------------------------------------------------
     def view(self, run: int) -> CacheView:
         return self._views[run]
+
+    def named_view(self, name: str) -> CacheView:
+        return self._named_views[name]
 
     def bytes(self) -> int:
         return sum(g.bytes() for g in self._kv_groups)

@@ -65,7 +65,7 @@ def add_request_flags(p):
 
 
 def build_parser(prog="burn-lm"):
-    ap = argparse.ArgumentParser(prog=prog, description="B200-native generation with the dense Llama decoder")
+    ap = argparse.ArgumentParser(prog=prog, description="B200-native generation with the registered decoder architectures (see `models`)")
     sub = ap.add_subparsers(dest="command")
     sub.add_parser("models", help="List the registered architectures")
     run = sub.add_parser("run", help="Run inference on a model folder in the terminal")

@@ -56,6 +56,32 @@ _PRESETS = {
 }
 
 
+def _fobilorn_layer(heads, kv_heads, dim, vdim, window, keep_first, mlp, v_mix=True):
+    return {"type": "attention", "mlp": mlp,
+            "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "v_mix": v_mix,
+                      "mask": {"size": window, "keep_first": keep_first}}}
+
+
+def _moe(experts, top, ff, shared_ff):
+    return {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff},
+            "shared": {"ff": shared_ff} if shared_ff else None}
+
+
+# a small Fobilorn decoder that uses every branch of the design: a dense and two mixture-of-experts layers (one
+# without a shared expert), a layer without a feed-forward, layers inside and outside the blending of values,
+# one and several kv heads, values wider and narrower than the keys
+_PRESETS["fobilorn_tiny"] = {
+    "architecture": "Fobilorn", "vocab": 384, "width": 96,
+    "embedding": {"bigram": {"buckets": 211, "mul_prev": 13, "mul_cur": 29}}, "norm": {"eps": 1e-5},
+    "layers": [
+        _fobilorn_layer(4, 2, 24, 16, 40, 6, {"kind": "dense", "ff": 160}),
+        _fobilorn_layer(6, 1, 16, 40, 24, 0, _moe(6, 2, 48, 64), v_mix=False),
+        _fobilorn_layer(4, 2, 32, 16, 70, 3, None),
+        _fobilorn_layer(2, 2, 24, 16, 33, 9, _moe(5, 1, 32, None)),
+    ],
+}
+
+
 def preset_names() -> list:
     return sorted(_PRESETS)
 

@@ -32,6 +32,8 @@ NVCC_FLAGS += os.environ.get("BURN_LM_B200_NVCC_FLAGS", "").split()
 MODULES = {
     "elementwise": ["elementwise.cu"],
     "attention": ["attention.cu"],
+    "attention_sink": ["attention_sink.cu"],
+    "moe": ["moe.cu"],
     "gemm": ["gemm_f32.cu"],
     "gemv": ["gemv.cu"],
     "gemm_tc": ["gemm_tc.cu"],

@@ -521,3 +521,122 @@ BLM_API int blm_decode_advance(int* tokens, int* pos, const int* sampled, int* h
     blm_launch_dependent(bump_kernel, dim3(1), dim3(1), 0, stream, step_no);
     return blm_check_launch("decode_advance");
 }
+
+// ---------------------------------------------------------------------------------------------
+// Token embedding plus a hashed embedding of the pair (previous token, token), optionally followed by the
+// Dynamic Tanh norm, into the fp32 residual stream.
+//   out[n, :] = table[tok] + pairs[row],  row = (prev * mul_prev + tok * mul_cur) mod buckets, and row `buckets`
+//   (the table's last) for the first token of a sequence.
+// The previous token of a row that continues its sequence inside this step is the row before it; for the first
+// row of a step's portion it is read from the sequence's paged line of token ids, to which every row appends its
+// own token at its position.  Rows of no sequence (token_seq < 0) take the last row and append nothing.
+// ---------------------------------------------------------------------------------------------
+template <typename TT>
+__global__ void embed_pairs_kernel(const int* __restrict__ tokens, const int* __restrict__ token_seq, const int* __restrict__ token_pos,
+                                   const int* __restrict__ cu_seqlens, const int* __restrict__ slot_of_seq,
+                                   const int* __restrict__ block_table, int table_stride, int* __restrict__ ids_pool, int page_size,
+                                   const TT* __restrict__ table, const TT* __restrict__ pairs, float* __restrict__ out, int width,
+                                   int vocab, long long buckets, long long mul_prev, long long mul_cur,
+                                   const float* __restrict__ norm_w, const float* __restrict__ norm_b, const float* __restrict__ norm_alpha) {
+    const int n = blockIdx.x;
+    int tok = tokens[n];
+    if ((unsigned)tok >= (unsigned)vocab) tok = 0;  // ids are validated on the host; never read wild
+    const int seq = token_seq[n];
+    long long row = buckets;
+    if (seq >= 0) {
+        const int pos = token_pos[n];
+        const size_t line = (size_t)slot_of_seq[seq] * table_stride;
+        if (pos > 0) {
+            int prev;
+            if (n > cu_seqlens[seq]) {
+                prev = tokens[n - 1];
+            } else {
+                const int page = block_table[line + (pos - 1) / page_size];
+                prev = ids_pool[(size_t)page * page_size + (pos - 1) % page_size];
+            }
+            if ((unsigned)prev >= (unsigned)vocab) prev = 0;
+            row = ((long long)prev * mul_prev + (long long)tok * mul_cur) % buckets;
+        }
+        if (threadIdx.x == 0) {
+            const int page = block_table[line + pos / page_size];
+            ids_pool[(size_t)page * page_size + pos % page_size] = tok;
+        }
+    }
+    const TT* a = table + (size_t)tok * width;
+    const TT* b = pairs + (size_t)row * width;
+    float* o = out + (size_t)n * width;
+    const float alpha = norm_w ? norm_alpha[0] : 0.f;
+    for (int d = threadIdx.x; d < width; d += blockDim.x) {
+        float v = to_f32(a[d]) + to_f32(b[d]);
+        if (norm_w) v = tanhf(alpha * v) * norm_w[d] + norm_b[d];
+        o[d] = v;
+    }
+}
+
+BLM_API int blm_embed_pairs(const int* tokens, const int* token_seq, const int* token_pos, const int* cu_seqlens, const int* slot_of_seq,
+                            const int* block_table, int table_stride, int* ids_pool, int page_size, const void* table,
+                            const void* pairs, int table_dtype, float* out, int n_tokens, int width, int vocab, long long buckets,
+                            long long mul_prev, long long mul_cur, const float* norm_w, const float* norm_b, const float* norm_alpha,
+                            cudaStream_t stream) {
+    if (n_tokens == 0) return BLM_OK;
+    BLM_REQUIRE(n_tokens > 0 && width > 0 && vocab > 0 && buckets > 0 && page_size > 0 && table_stride > 0, "embed_pairs: bad sizes");
+    BLM_REQUIRE(norm_w == nullptr || (norm_b != nullptr && norm_alpha != nullptr), "embed_pairs: the norm needs weight, bias and alpha");
+    const int threads = width >= 1024 ? 256 : 128;
+    if (table_dtype == BLM_F32)
+        embed_pairs_kernel<float><<<n_tokens, threads, 0, stream>>>(tokens, token_seq, token_pos, cu_seqlens, slot_of_seq, block_table,
+            table_stride, ids_pool, page_size, (const float*)table, (const float*)pairs, out, width, vocab, buckets, mul_prev, mul_cur,
+            norm_w, norm_b, norm_alpha);
+    else if (table_dtype == BLM_BF16)
+        embed_pairs_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(tokens, token_seq, token_pos, cu_seqlens, slot_of_seq,
+            block_table, table_stride, ids_pool, page_size, (const __nv_bfloat16*)table, (const __nv_bfloat16*)pairs, out, width, vocab,
+            buckets, mul_prev, mul_cur, norm_w, norm_b, norm_alpha);
+    else
+        return blm_fail(BLM_BAD_ARGUMENT, "embed_pairs: table dtype %d", table_dtype);
+    return blm_check_launch("embed_pairs");
+}
+
+// ---------------------------------------------------------------------------------------------
+// Residual add + Dynamic Tanh norm: no mean, no variance, so every element goes its own way.
+//   rows == nullptr: resid[n] += d0[n] + d1[n] + d2[n] (fp32, stored); out[n] = tanh(alpha resid[n]) * w + b
+//   rows != nullptr: out[i] from resid[rows[i]] + the deltas' rows[i]; resid is left as it is
+// Deltas may be null; out may be null (then the deltas are only added into the stream).  w, b, alpha are fp32.
+// ---------------------------------------------------------------------------------------------
+template <typename TA>
+__global__ void add_dyt_kernel(float* __restrict__ resid, const TA* __restrict__ d0, const TA* __restrict__ d1, const TA* __restrict__ d2,
+                               const float* __restrict__ w, const float* __restrict__ b, const float* __restrict__ alpha_p,
+                               TA* __restrict__ out, const int* __restrict__ rows, int width) {
+    const int src = rows ? rows[blockIdx.x] : blockIdx.x;
+    float* r = resid + (size_t)src * width;
+    const size_t off = (size_t)src * width;
+    const float alpha = out ? alpha_p[0] : 0.f;
+    const bool any = d0 || d1 || d2;
+    for (int d = threadIdx.x; d < width; d += blockDim.x) {
+        float h = r[d];
+        if (any) {
+            float s = 0.f;
+            if (d0) s = to_f32(d0[off + d]);
+            if (d1) s += to_f32(d1[off + d]);
+            if (d2) s += to_f32(d2[off + d]);
+            h += s;
+            if (!rows) r[d] = h;
+        }
+        if (out) out[(size_t)blockIdx.x * width + d] = from_f32<TA>(tanhf(alpha * h) * w[d] + b[d]);
+    }
+}
+
+BLM_API int blm_add_dyt(float* resid, const void* d0, const void* d1, const void* d2, const float* w, const float* b, const float* alpha,
+                        void* out, int act_dtype, const int* rows, int n_rows, int width, cudaStream_t stream) {
+    if (n_rows == 0) return BLM_OK;
+    BLM_REQUIRE(n_rows > 0 && width > 0, "add_dyt: bad sizes");
+    BLM_REQUIRE(out == nullptr || (w != nullptr && b != nullptr && alpha != nullptr), "add_dyt: the norm needs weight, bias and alpha");
+    const int threads = width >= 2048 ? 512 : 256;
+    if (act_dtype == BLM_F32)
+        add_dyt_kernel<float><<<n_rows, threads, 0, stream>>>(resid, (const float*)d0, (const float*)d1, (const float*)d2, w, b, alpha,
+                                                             (float*)out, rows, width);
+    else if (act_dtype == BLM_BF16)
+        add_dyt_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(resid, (const __nv_bfloat16*)d0, (const __nv_bfloat16*)d1,
+                                                                     (const __nv_bfloat16*)d2, w, b, alpha, (__nv_bfloat16*)out, rows, width);
+    else
+        return blm_fail(BLM_BAD_ARGUMENT, "add_dyt: activation dtype %d", act_dtype);
+    return blm_check_launch("add_dyt");
+}

@@ -65,9 +65,9 @@ class Engine:
             max_seq_len = model.plan.max_positions
         max_seq_len = min(max_seq_len, pages * page)
         self.cache = Cache(model.cache_needs(), model.plan.schedule, max_tokens, max_seqs, max_seq_len,
-                           rt.dtype, rt.device)
+                           rt.dtype, rt.device, named=model.named_cache_needs())
         self.workspace = Workspace(rt.device)
-        K.prebuild(rt.dtype)
+        K.prebuild(rt.dtype, model.kernel_modules())
         # tables of positions reach to the end of the last page, as the length buckets of captured steps do
         model.prepare(-(-self.cache.max_seq_len // page) * page)
         self.vocab_size = model.plan.vocab_size

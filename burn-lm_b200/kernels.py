@@ -81,6 +81,26 @@ _protos = {
         "blm_convert": [c_void_p, c_int, c_void_p, c_int, c_size_t, c_void_p],
         "blm_decode_advance": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
         "blm_step_tables": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+        "blm_embed_pairs": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                            c_int, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p,
+                            c_void_p],
+        "blm_add_dyt": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                        c_int, c_void_p],
+    },
+    "attention_sink": {
+        "blm_qk_norm_append": [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p,
+                               c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p, c_void_p, c_void_p,
+                               c_void_p, c_int, c_void_p],
+        "blm_attention_sink": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                               c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                               c_void_p],
+    },
+    "moe": {
+        "blm_moe_route": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+        "blm_moe_group": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+        "blm_moe_experts": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                            c_int, c_int, c_int, c_int, c_void_p],
+        "blm_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     },
     "attention": {
         "blm_attention": [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
@@ -140,10 +160,13 @@ def _lib(module: str) -> ctypes.CDLL:
     return lib
 
 
-def prebuild(dtype) -> None:
+def prebuild(dtype, modules=None) -> None:
     """Compile, side by side, the modules that every step of a model of this dtype uses, so that a first
-    call waits for the slowest of them instead of for their sum.  The others are still built when first used."""
-    _build.build_many(["elementwise", "attention", "gemv" if dtype == torch.bfloat16 else "gemm"])
+    call waits for the slowest of them instead of for their sum.  The others are still built when first used.
+    `modules`: the ones the model's parts name (their `kernel_modules`); None: those of the dense decoder."""
+    if modules is None:
+        modules = ["elementwise", "attention"]
+    _build.build_many(sorted(set(modules)) + ["gemv" if dtype == torch.bfloat16 else "gemm"])
 
 
 _launches = 0
@@ -212,6 +235,160 @@ def add_rmsnorm(resid, delta, gamma, eps, out, rows=None):
         raise KernelError("add_rmsnorm: rows must be int32")
     _call("elementwise", "blm_add_rmsnorm", _ptr(resid), _ptr(delta), _ptr(gamma), _code(gamma.dtype), _ptr(out),
           _code(out.dtype), _ptr(rows), n_out, d, c_float(eps), _stream())
+
+
+def embed_pairs(tokens, table, pairs, out, step, ids_pool, block_table, buckets, mul_prev, mul_cur, norm=None):
+    """out[n] = table[tokens[n]] + pairs[(previous token * mul_prev + token * mul_cur) mod buckets] as fp32 (the row
+    `buckets` for a sequence's first token), then, with `norm` = (weight, bias, alpha) in float32, tanh(alpha x) * weight
+    + bias.  The previous token of a portion's first row comes from the sequence's paged line of token ids `ids_pool`
+    (int32 [pages, PAGE], looked up through `block_table`), to which every row appends its own token.  `step`: the
+    step's tokens' sequences and positions (parts.base.StepContext)."""
+    _need_cuda(tokens, table, pairs, out, ids_pool, block_table)
+    n, (v, d) = tokens.numel(), table.shape
+    if tokens.dtype != torch.int32 or out.dtype != torch.float32 or tuple(out.shape) != (n, d):
+        raise KernelError("embed_pairs: tokens int32 [N], out float32 [N, D]")
+    if pairs.dtype != table.dtype or tuple(pairs.shape) != (buckets + 1, d):
+        raise KernelError(f"embed_pairs: the table of pairs must be [{buckets + 1}, {d}] in the token table's dtype")
+    if ids_pool.dtype != torch.int32 or ids_pool.dim() != 2 or ids_pool.shape[1] != PAGE:
+        raise KernelError(f"embed_pairs: the line of token ids must be int32 [pages, {PAGE}]")
+    w = b = a = None
+    if norm is not None:
+        w, b, a = norm
+        _need_cuda(w, b, a)
+        if not (w.dtype == b.dtype == a.dtype == torch.float32) or w.numel() != d or b.numel() != d or a.numel() != 1:
+            raise KernelError("embed_pairs: norm = (weight [D], bias [D], alpha []) in float32")
+    _call("elementwise", "blm_embed_pairs", _ptr(tokens), _ptr(step.token_seq), _ptr(step.token_pos), _ptr(step.cu_seqlens),
+          _ptr(step.slot_of_seq), _ptr(block_table), block_table.shape[1], _ptr(ids_pool), PAGE, _ptr(table), _ptr(pairs),
+          _code(table.dtype), _ptr(out), n, d, v, int(buckets), int(mul_prev), int(mul_cur), _ptr(w), _ptr(b), _ptr(a), _stream())
+
+
+def add_dyt(resid, deltas, weight, bias, alpha, out, rows=None):
+    """Residual add fused with the Dynamic Tanh norm, in fp32: the stream takes the sum of up to three `deltas`
+    (tensors of the activation dtype shaped like `resid`, or an empty list), then out = tanh(alpha x) * weight + bias.
+
+    rows is None: resid += sum(deltas) (stored); out[n] from every row.  rows given (int32 [R]): out[i] from row rows[i]
+    of resid + deltas; resid unchanged.  `out` None: the deltas are only added into the stream."""
+    deltas = [t for t in (deltas or ()) if t is not None]
+    _need_cuda(resid, weight, bias, alpha, out, rows, *deltas)
+    d = resid.shape[-1]
+    if len(deltas) > 3:
+        raise KernelError("add_dyt: at most three deltas")
+    if resid.dtype != torch.float32:
+        raise KernelError("add_dyt: resid float32 [N, D]")
+    act = out.dtype if out is not None else (deltas[0].dtype if deltas else torch.float32)
+    for t in deltas:
+        if t.dtype != act or t.shape != resid.shape:
+            raise KernelError("add_dyt: deltas must match resid's shape and the activation dtype")
+    n_out = rows.numel() if rows is not None else resid.shape[0]
+    if out is not None:
+        if tuple(out.shape) != (n_out, d) or weight.numel() != d or bias.numel() != d or alpha.numel() != 1 \
+                or not (weight.dtype == bias.dtype == alpha.dtype == torch.float32):
+            raise KernelError("add_dyt: out [rows, D]; weight [D], bias [D], alpha [] in float32")
+    if rows is not None and rows.dtype != torch.int32:
+        raise KernelError("add_dyt: rows must be int32")
+    ds = deltas + [None] * (3 - len(deltas))
+    _call("elementwise", "blm_add_dyt", _ptr(resid), _ptr(ds[0]), _ptr(ds[1]), _ptr(ds[2]), _ptr(weight), _ptr(bias), _ptr(alpha),
+          _ptr(out), _code(act), _ptr(rows), n_out, d, _stream())
+
+
+def kv_page_elems(n_kv, key_dim, value_dim) -> int:
+    """Elements of a cache page that holds its keys [n_kv, PAGE, key_dim] followed by its values [n_kv, PAGE, value_dim]."""
+    return n_kv * PAGE * (key_dim + value_dim)
+
+
+def _flat_pool(pool, n_kv, key_dim, value_dim):
+    elems = kv_page_elems(n_kv, key_dim, value_dim)
+    if not pool.is_contiguous() or pool.numel() != pool.shape[0] * elems:
+        raise KernelError(f"the cache pool must hold pages of {elems} elements ({n_kv} kv heads, keys of {key_dim}, values of {value_dim})")
+    return elems
+
+
+def qk_norm_append(proj, step, pool, block_table, q_out, n_heads, n_kv, key_dim, value_dim, q_weight=None, k_weight=None,
+                   eps=0.0, blend=None, values_in=None, values_out=None):
+    """What follows a fused projection [q | k | v | ...] (float32 [N, >= (n_heads + n_kv) key_dim + n_kv value_dim]):
+    q and k are each divided by the root mean square of their WHOLE row (all heads at once, eps inside the root) and
+    multiplied by `q_weight` / `k_weight` (float32; None: q and k stay as they are); v becomes (1 - blend) v + blend
+    values_in[n] when `values_in` (float32 [N, n_kv value_dim]) is given, `blend` a float32 scalar on the device;
+    `values_out` receives v; q goes to `q_out` [N, n_heads key_dim], k and v to the token's place in the paged cache."""
+    _need_cuda(proj, pool, block_table, q_out, q_weight, k_weight, blend, values_in, values_out)
+    n = proj.shape[0]
+    qc, kc, vc = n_heads * key_dim, n_kv * key_dim, n_kv * value_dim
+    if proj.dtype != torch.float32 or proj.dim() != 2 or proj.shape[1] < qc + kc + vc:
+        raise KernelError("qk_norm_append: the projection is float32 [N, q + k + v (+ more)]")
+    if tuple(q_out.shape) != (n, qc) or q_out.dtype != pool.dtype:
+        raise KernelError("qk_norm_append: q_out must be [N, heads * key_dim] in the cache's dtype")
+    for t, size in ((q_weight, qc), (k_weight, kc), (blend, 1), (values_in, n * vc), (values_out, n * vc)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != size):
+            raise KernelError("qk_norm_append: weights, blend and values are float32 of the sizes the head counts give")
+    _call("attention_sink", "blm_qk_norm_append", _ptr(proj), proj.stride(0), n, n_heads, n_kv, key_dim, value_dim, _ptr(q_weight),
+          _ptr(k_weight), c_float(eps), _ptr(blend), _ptr(values_in), _ptr(values_out), _ptr(q_out), _ptr(pool), _code(pool.dtype),
+          _flat_pool(pool, n_kv, key_dim, value_dim), PAGE, _ptr(step.token_seq), _ptr(step.token_pos), _ptr(step.slot_of_seq),
+          _ptr(block_table), block_table.shape[1], _stream())
+
+
+def attention_sink(q, step, pool, block_table, out, n_heads, n_kv, key_dim, value_dim, scale, window, keep_first=0, sink=True,
+                   gate=None, gate_stride=0):
+    """Attention of the step's tokens over the paged cache (after the append) where the query at position i sees the
+    key at j when j <= i and (i - j < window or j < keep_first); softmax with `sink` added to its denominator (one more
+    entry of score 0 without a value); keys of `key_dim` and values of `value_dim` lanes; `gate`: a float32 tensor
+    whose element n * gate_stride + h is squashed by a sigmoid and multiplies head h's output of token n.
+    q [N, n_heads key_dim] and out [N, n_heads value_dim] in the cache's dtype."""
+    _need_cuda(q, pool, block_table, out)
+    n = q.shape[0]
+    if tuple(q.shape) != (n, n_heads * key_dim) or tuple(out.shape) != (n, n_heads * value_dim) or q.dtype != pool.dtype \
+            or out.dtype != pool.dtype:
+        raise KernelError("attention_sink: q [N, heads * key_dim] and out [N, heads * value_dim] in the cache's dtype")
+    if gate is not None and (not gate.is_cuda or gate.dtype != torch.float32):
+        raise KernelError("attention_sink: the gate is float32")
+    _call("attention_sink", "blm_attention_sink", _ptr(q), _ptr(pool), _code(pool.dtype), _flat_pool(pool, n_kv, key_dim, value_dim),
+          _ptr(block_table), block_table.shape[1], _ptr(step.token_seq), _ptr(step.token_pos), _ptr(step.slot_of_seq), _ptr(gate),
+          int(gate_stride), _ptr(out), n, n_heads, n_kv, key_dim, value_dim, PAGE, int(window), int(keep_first), c_float(scale),
+          1 if sink else 0, _stream())
+
+
+def moe_route(h, router, top):
+    """(ids int32 [N, top], weights float32 [N, top]): every token's `top` experts of largest sigmoid(router h), in
+    falling order (the lower index on a tie), with those scores.  router float32 [experts, D]; sums in float32."""
+    _need_cuda(h, router)
+    n, d = h.shape
+    if router.dtype != torch.float32 or router.dim() != 2 or router.shape[1] != d:
+        raise KernelError("moe_route: the router is float32 [experts, D]")
+    ids = torch.empty((n, top), dtype=torch.int32, device=h.device)
+    weights = torch.empty((n, top), dtype=torch.float32, device=h.device)
+    _call("moe", "blm_moe_route", _ptr(h), _code(h.dtype), _ptr(router), n, d, router.shape[0], top, _ptr(ids), _ptr(weights), _stream())
+    return ids, weights
+
+
+def moe_experts(h, ids, weights, gate_up, down, extra=None, weight_on_input=True):
+    """sum over a token's chosen experts of expert(weight h) (`weight_on_input`) or of weight expert(h), plus `extra`
+    [N, D] when given; expert(x) = down[e] (silu(gate[e] x) * (up[e] x)).  gate_up [experts, 2 ff, D] (an expert's
+    gate rows, then its up rows) and down [experts, D, ff] in h's dtype.  Returns [N, D] in h's dtype."""
+    _need_cuda(h, ids, weights, gate_up, down, extra)
+    n, d = h.shape
+    top = ids.shape[1]
+    e, two_ff, _ = gate_up.shape
+    ff = two_ff // 2
+    if gate_up.dtype != h.dtype or down.dtype != h.dtype or tuple(gate_up.shape) != (e, 2 * ff, d) or tuple(down.shape) != (e, d, ff):
+        raise KernelError("moe_experts: gate_up [experts, 2 ff, D] and down [experts, D, ff] in the activations' dtype")
+    if ids.dtype != torch.int32 or weights.dtype != torch.float32 or tuple(weights.shape) != (n, top):
+        raise KernelError("moe_experts: ids int32 [N, top], weights float32 [N, top]")
+    if extra is not None and (extra.dtype != h.dtype or tuple(extra.shape) != (n, d)):
+        raise KernelError("moe_experts: extra must be [N, D] in the activations' dtype")
+    dev = h.device
+    pairs = n * top
+    offsets = torch.empty(e + 1, dtype=torch.int32, device=dev)
+    order = torch.empty(pairs, dtype=torch.int32, device=dev)
+    place_of = torch.empty(pairs, dtype=torch.int32, device=dev)
+    act = torch.empty((pairs, ff), dtype=h.dtype, device=dev)
+    y = torch.empty((pairs, d), dtype=torch.float32, device=dev)
+    out = torch.empty((n, d), dtype=h.dtype, device=dev)
+    stream = _stream()
+    _call("moe", "blm_moe_group", _ptr(ids), pairs, e, _ptr(offsets), _ptr(order), _ptr(place_of), stream)
+    _call("moe", "blm_moe_experts", _ptr(h), _code(h.dtype), _ptr(weights), _ptr(order), _ptr(offsets), _ptr(gate_up), _ptr(down),
+          _ptr(act), _ptr(y), n, d, ff, e, top, 1 if weight_on_input else 0, stream, kernels=2)
+    _call("moe", "blm_moe_combine", _ptr(y), _ptr(place_of), _ptr(weights), _ptr(extra), _ptr(out), _code(h.dtype), n, d, top,
+          0 if weight_on_input else 1, stream)
+    return out
 
 
 def rope_table(inv_freq, n_positions):

@@ -118,6 +118,19 @@ class Model:
         return [None if e.cache_of is not None else self.layers[e.layer].cache_need()
                 for e in self.plan.schedule]
 
+    def named_cache_needs(self) -> dict:
+        """What parts outside the layers keep per sequence, by the name of their view of the cache."""
+        if hasattr(self.embedding, "cache_need"):
+            return {"embedding": self.embedding.cache_need()}
+        return {}
+
+    def kernel_modules(self) -> list:
+        """The kernel modules the parts of this model name (for compiling them side by side before the first step)."""
+        names = set()
+        for p in self.parts() + [layer.block for layer in self.layers]:
+            names.update(getattr(p, "kernel_modules", ("elementwise",)))
+        return sorted(names)
+
     # -- forward ---------------------------------------------------------------------------------
     def forward(self, step, cache):
         """Logits (fp32 [n_want, vocab]) at the wanted rows of the step, or None when none is wanted."""
@@ -134,6 +147,8 @@ class Model:
                 step.handoff = NormHandoff()
             step.handoff.expect(first.first_norm())
             self.embedding.forward(step.tokens, resid, handoff=step.handoff)
+        elif getattr(self.embedding, "takes_step", False):
+            self.embedding.forward(step.tokens, resid, step=step, cache=cache.named_view("embedding"))
         else:
             self.embedding.forward(step.tokens, resid)
         if self.stream_position is not None:

@@ -41,6 +41,7 @@ class Attention(Part):
     family = "mixer"
     graph_safe = True
     roles = ("q", "k", "v", "o")
+    kernel_modules = ("elementwise", "attention")
 
     def __init__(self, spec, tensors, runtime):
         super().__init__(spec, tensors, runtime)

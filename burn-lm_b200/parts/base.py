@@ -10,14 +10,17 @@ Interfaces by family (registered with `registry.register_part(family, kind)`):
   norm          add_norm(resid, delta, rows=None) -> normed activations.  `resid` is the fp32 residual
                 stream [N, D]; the norm first adds `delta` (the previous part's output, or None) into
                 it, in fp32, then normalises.  With `rows` it does so for those rows only, into a
-                new tensor, and leaves `resid` alone.
+                new tensor, and leaves `resid` alone.  A norm that sets `takes_several` also takes a tuple of
+                outputs as `delta` (the branches of a block whose parts run side by side) and adds them all.
   mixer         cache_need() -> CacheNeed;  forward(x, step, cache_view) -> [N, D] in the compute dtype.
   feed_forward  forward(x, step) -> [N, D].
   position      a constant-holder the mixer asks: rotation() -> (inv_freq float64 tensor or None,
                 rotary_dim, interleaved);  on_embedding(resid, step) for encodings added to the stream.
   block         forward(resid, delta, step, cache_view) -> delta: how norms, mixer and feed-forward
                 are arranged around the residual stream.
-  embedding     forward(tokens, out) fills the fp32 residual stream.
+  embedding     forward(tokens, out) fills the fp32 residual stream.  One that sets `takes_step` gets the step and
+                its own view of the cache as well (forward(tokens, out, step=, cache=)) and says what it keeps per
+                sequence with cache_need().
   head          forward(x) -> fp32 logits.
 """
 from __future__ import annotations
@@ -43,8 +46,10 @@ class Runtime:
 class CacheNeed:
     """What one run of a mixer keeps per sequence.
 
-    kind "kv":    keys and values per position: n_kv_heads x head_dim each; `window` None keeps all
-                  positions, a number keeps that many of the latest.
+    kind "kv":    keys and values per position: n_kv_heads x head_dim each (values of `value_dim` lanes when
+                  that is set and differs); `window` None keeps all positions, a number keeps that many of the
+                  latest, and beside them the first `keep_first` positions of the sequence.
+    kind "ids":   one int32 per position (a token id, say), paged like keys and values; `window` as above.
     kind "state": a fixed-size block per sequence of `state_shape` in `state_dtype`, zero when a
                   sequence starts.
     kind "none":  nothing."""
@@ -54,6 +59,8 @@ class CacheNeed:
     window: Optional[int] = None
     state_shape: tuple = ()
     state_dtype: str = "float32"
+    value_dim: Optional[int] = None
+    keep_first: int = 0
 
 
 @dataclass

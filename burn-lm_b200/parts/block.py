@@ -1,4 +1,5 @@
-"""How a layer's parts stand around the residual stream.
+"""How a layer's parts stand around the residual stream: one after the other behind norms of their own
+(pre-norm), or side by side behind one norm (parallel).
 
 Pre-norm: h = x + mixer(norm(x)); out = h + feed_forward(norm(h))
 (crates/burn-lm-llama/src/nn/transformer.rs:241-256).  The residual stream is fp32; a part's
@@ -7,6 +8,7 @@ the block before it (`delta`) and returns its own.
 """
 from __future__ import annotations
 
+from .. import kernels as K
 from ..registry import register_part
 from .linear import NormHandoff
 
@@ -55,3 +57,46 @@ class PreNormBlock:
             handoff.expect(next_norm)
             return ff.forward(x, step, stream=resid)
         return ff.forward(x, step)
+
+
+@register_part("block", "parallel")
+class ParallelBlock:
+    """h = norm(x); x <- x + (mixer(h) + feed_forward(h)): one norm, and both parts read its output.  The layer
+    may have no feed-forward.  What the parts return is handed, as a tuple, to the norm that reads the stream next
+    when that norm adds several outputs at once (`takes_several`); else it is added into the stream here."""
+    family = "block"
+    graph_safe = True
+
+    NAMES = ("norm", "mixer", "feed_forward")
+
+    def __init__(self, parts: dict):
+        if not {"norm", "mixer"} <= set(parts) <= set(self.NAMES):
+            raise ValueError(f"the parallel block arranges parts named {self.NAMES} (the last may be absent); the layer has {sorted(parts)}")
+        self.norm, self.mixer, self.feed_forward = parts["norm"], parts["mixer"], parts.get("feed_forward")
+
+    def first_norm(self):
+        return self.norm
+
+    def forward(self, resid, delta, step, cache_view, next_norm=None):
+        if getattr(step, "handoff", None) is not None:
+            step.handoff.expect(None)          # no product of this block prepares a norm's input
+        h = self.norm.add_norm(resid, delta)
+        if not isinstance(h, type(resid)):
+            h = h.materialize()                # both parts read it
+        pending = []
+        mixer, ff = self.mixer, self.feed_forward
+        a = mixer.forward(h, step, cache_view, stream=resid) if getattr(mixer, "adds_to_stream", False) else mixer.forward(h, step, cache_view)
+        if a is not None:
+            pending.append(a)
+        if ff is not None:
+            f = ff.forward(h, step, stream=resid) if getattr(ff, "adds_to_stream", False) else ff.forward(h, step)
+            if f is not None:
+                pending.append(f)
+        if not pending:
+            return None
+        if len(pending) == 1:
+            return pending[0]
+        if getattr(next_norm, "takes_several", False):
+            return tuple(pending)
+        K.add_dyt(resid, pending, None, None, None, None)     # only the sum into the stream
+        return None

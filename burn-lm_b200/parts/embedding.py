@@ -8,10 +8,13 @@ from dataclasses import dataclass
 
 import torch
 
+from typing import Optional
+
 from .. import kernels as K
-from ..registry import register_part
+from ..plan import PartPlan
+from ..registry import part_class, register_part
 from ..weights.loader import TensorSpec
-from .base import Part
+from .base import CacheNeed, Part
 from .linear import HandedNorm, Linear
 
 
@@ -48,6 +51,57 @@ class Embedding(Part):
             handoff.leave(out, norm.gamma, handed)
             return
         K.embed(tokens, self.table, out)
+
+
+@dataclass(frozen=True)
+class PairEmbeddingSpec:
+    vocab_size: int
+    hidden_size: int
+    buckets: int                       # rows of the table of pairs, not counting its last row (a sequence's first token)
+    mul_prev: int
+    mul_cur: int
+    norm: Optional[PartPlan] = None    # family "norm": applied to the sum before it enters the stream
+
+
+@register_part("embedding", "token_pairs")
+class PairEmbedding(Part):
+    """x = table[token] + pairs[(previous token * mul_prev + token * mul_cur) mod buckets], the table's last row for a
+    sequence's first token, then an optional norm.  The previous token is part of what a sequence keeps: the part
+    asks the cache for a paged line of token ids, one per position, so that a step repeated or run ahead and
+    forgotten leaves nothing wrong behind, as with keys and values."""
+    family = "embedding"
+    graph_safe = True
+    roles = ("table", "pairs")
+    kernel_modules = ("elementwise",)
+    takes_step = True
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.norm = None
+        if spec.norm is not None:
+            self.norm = part_class("norm", spec.norm.kind)(spec.norm.spec, spec.norm.tensors, runtime)
+            if not hasattr(self.norm, "parameters"):
+                raise ValueError(f"the embedding applies its norm in its own kernel, which knows 'dynamic_tanh'; got {spec.norm.kind!r}")
+
+    def tensor_specs(self):
+        s, t = self.spec, self.tensor_names
+        return [TensorSpec(t["table"], (s.vocab_size, s.hidden_size)), TensorSpec(t["pairs"], (s.buckets + 1, s.hidden_size))] \
+            + (self.norm.tensor_specs() if self.norm is not None else [])
+
+    def bind(self, loaded):
+        self.table, self.pairs = loaded[self.tensor_names["table"]], loaded[self.tensor_names["pairs"]]
+        if self.table.dtype != self.pairs.dtype:
+            raise ValueError(f"{self.tensor_names['table']} and {self.tensor_names['pairs']} are stored in different dtypes")
+        if self.norm is not None:
+            self.norm.bind(loaded)
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed("ids", window=2)       # a coming token looks one position back
+
+    def forward(self, tokens, out, step=None, cache=None):
+        s = self.spec
+        K.embed_pairs(tokens, self.table, self.pairs, out, step, cache.pool, cache.block_table, s.buckets, s.mul_prev, s.mul_cur,
+                      norm=self.norm.parameters() if self.norm is not None else None)
 
 
 @dataclass(frozen=True)

@@ -1,0 +1,87 @@
+"""The mixture-of-experts feed-forward: a router picks `top` of `n_experts` small gated feed-forwards per token.
+
+Router logits z = W_router h in fp32, scores s = sigmoid(z); the `top` experts of largest score are chosen (the
+lower index on a tie) and weighted by those scores as they are, not renormalised.  With `weight_on` "input" the
+weight multiplies the expert's input, out = sum expert(s h); with "output" its result, out = sum s expert(h).
+expert(x) = W_down (silu(W_gate x) * (W_up x)), without biases.  A shared feed-forward (any registered kind) may run
+for every token beside them; its result is added.
+
+Everything stays on the device: the pairs (token, expert) are grouped by expert and the experts run as grouped
+products over them, so a step can be captured in a CUDA graph.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from .. import kernels as K
+from ..plan import PartPlan
+from ..registry import part_class, register_part
+from ..weights.loader import TensorSpec
+from .base import Part
+
+
+@dataclass(frozen=True)
+class SigmoidMoESpec:
+    hidden_size: int
+    n_experts: int
+    top: int
+    expert_size: int                       # inner size of one expert
+    weight_on: str = "input"               # "input" or "output"
+    shared: Optional[PartPlan] = None      # family "feed_forward": runs for every token
+
+
+@register_part("feed_forward", "sigmoid_moe")
+class SigmoidMoE(Part):
+    """tensors: "router"; "gate", "up", "down": the experts' stored names with {} where the expert's number stands."""
+    family = "feed_forward"
+    graph_safe = True
+    roles = ("router", "gate", "up", "down")
+    kernel_modules = ("elementwise", "moe")
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        if spec.weight_on not in ("input", "output"):
+            raise ValueError(f"weight_on is 'input' or 'output', not {spec.weight_on!r}")
+        if not 1 <= spec.top <= spec.n_experts:
+            raise ValueError(f"top {spec.top} of {spec.n_experts} experts")
+        self.shared = None
+        if spec.shared is not None:
+            self.shared = part_class("feed_forward", spec.shared.kind)(spec.shared.spec, spec.shared.tensors, runtime)
+
+    def _names(self, role):
+        return [self.tensor_names[role].format(e) for e in range(self.spec.n_experts)]
+
+    def tensor_specs(self):
+        s = self.spec
+        specs = [TensorSpec(self.tensor_names["router"], (s.n_experts, s.hidden_size), init="normal:0.1")]
+        for g, u, d in zip(self._names("gate"), self._names("up"), self._names("down")):
+            specs += [TensorSpec(g, (s.expert_size, s.hidden_size)), TensorSpec(u, (s.expert_size, s.hidden_size)),
+                      TensorSpec(d, (s.hidden_size, s.expert_size))]
+        return specs + (self.shared.tensor_specs() if self.shared is not None else [])
+
+    def bind(self, loaded):
+        self.router = loaded[self.tensor_names["router"]].to(torch.float32).contiguous()
+        dt = self.runtime.dtype
+        gates, ups, downs = ([loaded[n].to(dt) for n in self._names(r)] for r in ("gate", "up", "down"))
+        # one tensor for all experts: [experts, gate rows then up rows, width] and [experts, width, inner]
+        self.gate_up = torch.stack([torch.cat([g, u], dim=0) for g, u in zip(gates, ups)]).contiguous()
+        self.down = torch.stack(downs).contiguous()
+        if self.shared is not None:
+            self.shared.bind(loaded)
+
+    def forward(self, x, step, stream=None):
+        ids, weights = K.moe_route(x, self.router, self.spec.top)
+        extra = None
+        if self.shared is not None:
+            # a shared part that can add into the stream itself does so (x is already there for both); else its result
+            # rides along into the sum
+            if stream is not None and getattr(self.shared, "adds_to_stream", False):
+                extra = self.shared.forward(x, step, stream=stream)
+            else:
+                extra = self.shared.forward(x, step)
+        return K.moe_experts(x, ids, weights, self.gate_up, self.down, extra=extra, weight_on_input=self.spec.weight_on == "input")
+
+    adds_to_stream = True

@@ -1,4 +1,4 @@
-"""RMS norm fused with the residual add.
+"""Norms fused with the residual add: RMS norm, and Dynamic Tanh (which takes no statistics).
 
 y = x / sqrt(mean(x^2) + eps) * gamma; it stands before the mixer, before the feed-forward and once
 after the last block (crates/burn-lm-llama/src/nn/transformer.rs:248-255,101; eps at :60-62 and
@@ -47,4 +47,42 @@ class RMSNorm(Part):
         n = rows.numel() if rows is not None else resid.shape[0]
         out = torch.empty((n, self.spec.size), dtype=self.runtime.dtype, device=resid.device)
         K.add_rmsnorm(resid, delta, self.gamma, self.spec.eps, out, rows)
+        return out
+
+
+@dataclass(frozen=True)
+class DynamicTanhSpec:
+    size: int
+
+
+@register_part("norm", "dynamic_tanh")
+class DynamicTanh(Part):
+    """y = tanh(alpha x) * weight + bias with a learned scalar alpha: a squashing in the place of a norm, computed
+    element by element in fp32 without a mean or a variance.  Weight, bias and alpha are kept in float32."""
+    family = "norm"
+    graph_safe = True
+    roles = ("weight", "bias", "alpha")
+    kernel_modules = ("elementwise",)
+    takes_several = True          # `delta` may be a tuple of outputs that are all added into the stream
+
+    def tensor_specs(self):
+        t, n = self.tensor_names, self.spec.size
+        return [TensorSpec(t["weight"], (n,), init="one_plus_normal:0.1"), TensorSpec(t["bias"], (n,), init="normal:0.1"),
+                TensorSpec(t["alpha"], (), init="one_plus_normal:0.2")]
+
+    def bind(self, loaded):
+        t = self.tensor_names
+        self.weight = loaded[t["weight"]].to(torch.float32).contiguous()
+        self.bias = loaded[t["bias"]].to(torch.float32).contiguous()
+        self.alpha = loaded[t["alpha"]].to(torch.float32).reshape(1).contiguous()
+
+    def parameters(self):
+        """(weight, bias, alpha) in float32, for a kernel that applies this norm in its own epilogue."""
+        return self.weight, self.bias, self.alpha
+
+    def add_norm(self, resid, delta, rows=None, lazy=False, handoff=None):
+        deltas = list(delta) if isinstance(delta, (tuple, list)) else ([delta] if delta is not None else [])
+        n = rows.numel() if rows is not None else resid.shape[0]
+        out = torch.empty((n, self.spec.size), dtype=self.runtime.dtype, device=resid.device)
+        K.add_dyt(resid, deltas, self.weight, self.bias, self.alpha, out, rows)
         return out
