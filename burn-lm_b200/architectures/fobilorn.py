@@ -11,6 +11,7 @@ Every layer brings its own sizes.  Stored names: 'embed', 'bigram', 'embed.norm'
 from __future__ import annotations
 
 from ..config.fobilorn import FobilornConfig
+from ..config.reader import ConfigError
 from ..parts.embedding import HeadSpec, PairEmbeddingSpec
 from ..parts.feed_forward import SwiGLUSpec
 from ..parts.moe import SigmoidMoESpec
@@ -34,6 +35,7 @@ def fobilorn_plan(cfg: FobilornConfig) -> ModelPlan:
     width = cfg.width
     layers = []
     blends = False       # whether an earlier layer already is the source of blended values
+    blended = None       # lanes of those values (kv heads x value size): the same in every layer that blends
     for i, layer in enumerate(cfg.layers):
         p, m = f"l{i}.", layer.mixer
         tensors = {"q": p + "mix.q", "k": p + "mix.k", "v": p + "mix.v", "o": p + "mix.o", "g": p + "mix.g",
@@ -42,6 +44,10 @@ def fobilorn_plan(cfg: FobilornConfig) -> ModelPlan:
         if m.v_mix:
             blend = "blend" if blends else "source"
             blends = True
+            if blended is not None and blended != m.kv_heads * m.vdim:
+                raise ConfigError(f"config key 'layers[{i}].mixer': v_mix blends values of {m.kv_heads} x {m.vdim} lanes with "
+                                  f"the {blended} lanes of the first layer that has v_mix")
+            blended = m.kv_heads * m.vdim
             tensors["blend"] = p + "mix.vmix"      # stored in the source layer too, where nothing reads it
         parts = [NamedPart("norm", "norm", _norm(width, p + "norm1")),
                  NamedPart("mixer", "mixer", PartPlan("sink_attention", SinkAttentionSpec(

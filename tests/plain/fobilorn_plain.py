@@ -84,6 +84,18 @@ def sink_softmax(scores, mask):
     return e / (np.exp(-m) + e.sum(axis=-1, keepdims=True))
 
 
+def attend(q, k, v, scale, window, keep_first, sink=True):
+    """One head: q [T, dk], k [T, dk], v [T, dv], the row t at position t.  Returns [T, dv]."""
+    T = q.shape[0]
+    mask = np.array([[visible(i, j, window, keep_first) for j in range(T)] for i in range(T)])
+    s = (q @ k.T) * scale
+    if sink:
+        return sink_softmax(s, mask) @ v
+    s = np.where(mask, s, -np.inf)
+    e = np.exp(s - s.max(axis=-1, keepdims=True))
+    return (e / e.sum(axis=-1, keepdims=True)) @ v
+
+
 def attention(h, w, spec, eps, v_first=None, mixes=False):
     """The attention mixer on the normed input h [T, D].  `w`: the layer's tensors by short name (q, k, v,
     q.norm, k.norm, vmix, g, o).  `spec`: heads, kv_heads, dim, vdim, scale, mask.size, mask.keep_first.
@@ -104,14 +116,11 @@ def attention(h, w, spec, eps, v_first=None, mixes=False):
     k = k.reshape(T, G, dk)
     vh = v.reshape(T, G, dv)
     window, keep = spec["mask"]["size"], spec["mask"]["keep_first"]
-    mask = np.array([[visible(i, j, window, keep) for j in range(T)] for i in range(T)])
     gate = sigmoid(h @ w["g"].T)                      # [T, H]
     out = np.zeros((T, H, dv))
     for head in range(H):
         kv = head // (H // G)
-        s = (q[:, head] @ k[:, kv].T) * spec["scale"]
-        p = sink_softmax(s, mask)
-        out[:, head] = (p @ vh[:, kv]) * gate[:, head:head + 1]
+        out[:, head] = attend(q[:, head], k[:, kv], vh[:, kv], spec["scale"], window, keep) * gate[:, head:head + 1]
     return out.reshape(T, H * dv) @ w["o"].T, v
 
 
@@ -130,13 +139,16 @@ def route(h, router, top):
     return order, np.take_along_axis(s, order, axis=-1)
 
 
-def moe_ff(h, w, n_experts, top, has_shared):
-    """Sum over a token's chosen experts of expert(weight * h), plus the shared expert on h."""
+def moe_ff(h, w, n_experts, top, has_shared, on_input=True):
+    """Sum over a token's chosen experts of expert(weight * h), plus the shared expert on h.  (`on_input` False: the
+    weight multiplies the expert's output instead, which the design does not do; the product's part has both.)"""
     chosen, weight = route(h, w["router"], top)
     out = np.zeros_like(h)
     for t in range(h.shape[0]):
         for e, s in zip(chosen[t], weight[t]):
-            out[t] += gated_ff(s * h[t:t + 1], w[f"e{e}.gate"], w[f"e{e}.up"], w[f"e{e}.down"])[0]
+            x = s * h[t:t + 1] if on_input else h[t:t + 1]
+            y = gated_ff(x, w[f"e{e}.gate"], w[f"e{e}.up"], w[f"e{e}.down"])[0]
+            out[t] += y if on_input else s * y
     if has_shared:
         out = out + gated_ff(h, w["shared.gate"], w["shared.up"], w["shared.down"])
     return out
