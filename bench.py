@@ -1,6 +1,7 @@
 """Decode and prefill throughput of the Llama-3.2-1B shape with random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--config 1b|3b|8b]
+    python bench.py --compare fobilorn [--size 1b-layers|8b-layers]     (another design beside this one, see run_compare)
 
 A "step" is one decode step of the whole batch.  The default run has the layer sizes of the 1B
 configuration (16 layers, width 2048, 32 heads on 8 kv heads of 64, inner 8192, vocabulary 128256,
@@ -274,6 +275,161 @@ def sweep(engine, cfg, pk):
                                       "frac_bf16": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 3)}}), flush=True)
 
 
+# ---------------------------------------------------------------------------------------------------------
+# --compare fobilorn: the Fobilorn decoder beside the dense Llama decoder at equal layer sizes
+# ---------------------------------------------------------------------------------------------------------
+COMPARE_SIZES = {
+    # name: width, heads, kv heads, head size, inner size, layers, vocabulary, window, kept first, experts, top
+    "1b-layers": dict(width=2048, heads=32, kv=8, hd=64, inner=8192, layers=4, vocab=32000, window=1024, keep=64, experts=16, top=2),
+    "8b-layers": dict(width=4096, heads=32, kv=8, hd=128, inner=14336, layers=2, vocab=32000, window=1024, keep=64, experts=16, top=2),
+}
+
+
+def compare_configs(z):
+    """(llama, fobilorn with dense feed-forwards, fobilorn with experts) of one size.  The experts' layers keep the
+    inner size a token uses: `top` experts of inner / (2 top) each beside a shared one of inner / 2."""
+    llama = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": z["layers"], "hidden_size": z["width"],
+             "num_attention_heads": z["heads"], "num_key_value_heads": z["kv"], "head_dim": z["hd"], "intermediate_size": z["inner"],
+             "vocab_size": z["vocab"], "rope_theta": 500000.0, "rope_scaling": None, "rms_norm_eps": 1e-5,
+             "tie_word_embeddings": False, "max_position_embeddings": 8192, "hidden_act": "silu"}
+
+    def fob(mlp):
+        layer = {"type": "attention", "mlp": mlp,
+                 "mixer": {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["hd"], "vdim": z["hd"], "scale": z["hd"] ** -0.5,
+                           "v_mix": True, "mask": {"size": z["window"], "keep_first": z["keep"]}}}
+        return {"architecture": "Fobilorn", "vocab": z["vocab"], "width": z["width"],
+                "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}}, "norm": {"eps": 1e-6},
+                "layers": [layer] * z["layers"]}
+    each = z["inner"] // (2 * z["top"])
+    return {"llama": llama, "fobilorn-dense": fob({"kind": "dense", "ff": z["inner"]}),
+            "fobilorn-experts": fob({"kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}, "expert": {"ff": each},
+                                     "shared": {"ff": z["inner"] // 2}})}
+
+
+def _time(fn, reps=10):
+    import torch
+    for _ in range(3):
+        fn()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(reps):
+        fn()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / reps
+
+
+def compare_kernels(z, pk):
+    """The new design's kernels alone beside the like kernels of the dense decoder, CUDA events, back to back: prompt
+    attention (one 2,048-token prompt), decode attention (64 sequences of 1,088 tokens) and the feed-forward of a
+    token's share of experts beside the dense products of the same inner size (2,048 and 64 tokens)."""
+    import torch
+    from types import SimpleNamespace
+    from burn_lm_b200 import kernels as K
+    dev, bf = "cuda", torch.bfloat16
+    H, G, hd, d = z["heads"], z["kv"], z["hd"], z["width"]
+    out = {}
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+
+    def attention_case(n_seqs, new, cached):
+        total = cached + new
+        pages_each = -(-total // K.PAGE)
+        n = n_seqs * new
+        bt = torch.arange(n_seqs * pages_each, dtype=torch.int32, device=dev).reshape(n_seqs, pages_each)
+        seq = [s for s in range(n_seqs) for _ in range(new)]
+        pos = [cached + t for _ in range(n_seqs) for t in range(new)]
+        st = SimpleNamespace(token_seq=i32(seq), token_pos=i32(pos), slot_of_seq=i32(list(range(n_seqs))),
+                             cu_seqlens=i32([new * s for s in range(n_seqs + 1)]), start_pos=i32([cached] * n_seqs))
+        q = torch.randn((n, H * hd), dtype=bf, device=dev)
+        # the dense decoder's kernel: window as the new design's, no kept first tokens
+        pool5 = torch.randn((n_seqs * pages_each, 2, G, K.PAGE, hd), dtype=bf, device=dev)
+        o = torch.empty_like(q)
+        splits = 1
+        ms_llama = _time(lambda: K.attention(q, q.shape[1], pool5, bt, st.cu_seqlens, st.slot_of_seq, st.start_pos, o, n, n_seqs, new,
+                                             H, G, hd, hd ** -0.5, window=z["window"], n_splits=splits, max_kv_len=total))
+        pool = pool5.reshape(n_seqs * pages_each, -1)
+        gate = torch.randn((n, H), dtype=torch.float32, device=dev)
+        ms_new = _time(lambda: K.attention_sink(q, st, pool, bt, o, H, G, hd, hd, hd ** -0.5, z["window"], z["keep"], sink=True,
+                                                gate=gate, gate_stride=H, max_q_len=new))
+        return ms_llama, ms_new, n, total
+
+    # prompt: flops of the visible pairs (window and causal), both products
+    ms_l, ms_n, n, total = attention_case(1, 2048, 0)
+    pairs = sum(min(t + 1, z["window"]) for t in range(2048))
+    flops = 4.0 * H * hd * pairs
+    out["attention_prefill_2048"] = {"llama_ms": round(ms_l, 4), "fobilorn_ms": round(ms_n, 4),
+                                     "llama_frac_bf16": round(flops / (ms_l / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+                                     "fobilorn_frac_bf16": round(flops / (ms_n / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+    ms_l, ms_n, n, total = attention_case(64, 1, 1087)
+    seen = min(total, z["window"])
+    nbytes = 64 * G * seen * 2 * hd * 2
+    out["attention_decode_b64"] = {"llama_ms": round(ms_l, 4), "fobilorn_ms": round(ms_n, 4), "keys_seen": seen,
+                                   "llama_frac_hbm": round(nbytes / (ms_l / 1e3) / 1e9 / pk["hbm_gbs"], 4),
+                                   "fobilorn_frac_hbm": round(nbytes / (ms_n / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
+    # feed-forward: a token's experts beside dense products of the inner size they make together
+    E, top = z["experts"], z["top"]
+    each = z["inner"] // (2 * top)
+    gate_up = torch.randn((E, 2 * each, d), dtype=bf, device=dev) * 0.02
+    down = torch.randn((E, d, each), dtype=bf, device=dev) * 0.02
+    router = torch.randn((E, d), dtype=torch.float32, device=dev)
+    w1 = torch.randn((2 * top * each, d), dtype=bf, device=dev) * 0.02
+    w2 = torch.randn((d, top * each), dtype=bf, device=dev) * 0.02
+    for n in (2048, 64):
+        h = torch.randn((n, d), dtype=bf, device=dev)
+        ids, weights = K.moe_route(h, router, top)
+        ms_moe = _time(lambda: K.moe_experts(h, ids, weights, gate_up, down))
+        a = torch.empty((n, top * each), dtype=bf, device=dev)
+
+        def dense():
+            gu = torch.mm(h, w1.t())
+            K.swiglu(gu, a)
+            return torch.mm(a, w2.t())
+        ms_dense = _time(dense)
+        flops = 2.0 * n * top * 3 * each * d
+        wbytes = 2.0 * 3 * each * d * min(E, n * top)             # the weights of the experts that get a token
+        out[f"experts_{n}_tokens"] = {
+            "fobilorn_ms": round(ms_moe, 4), "dense_same_inner_ms": round(ms_dense, 4),
+            "fobilorn_frac_bf16": round(flops / (ms_moe / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+            "dense_frac_bf16": round(flops / (ms_dense / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+            "fobilorn_frac_hbm": round(wbytes / (ms_moe / 1e3) / 1e9 / pk["hbm_gbs"], 4),
+            "dense_frac_hbm": round(2.0 * 3 * top * each * d / (ms_dense / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
+    return out
+
+
+def run_compare(args):
+    """One JSON line per size and model: prefill of one 2,048-token prompt and decode at batch 8 and 64 after 512-token
+    prompts, for the dense Llama decoder and the Fobilorn decoder (dense feed-forwards, and experts) at equal layer
+    sizes with random weights; then a line with the kernels alone."""
+    import torch
+    import burn_lm_b200 as blm
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device: burn-lm_b200 has no CPU path"}))
+        return 1
+    pk = peaks()
+    for size, z in COMPARE_SIZES.items():
+        if args.size and size != args.size:
+            continue
+        for name, cfg in compare_configs(z).items():
+            vocab = z["vocab"]
+            lm = blm.load_random(cfg, seed=0, dtype="bfloat16", max_seq_len=4096, max_batch=64, max_tokens=64 * 1024)
+            engine = lm.engine
+            line = {"compare": size, "model": name, "layers": z["layers"]}
+            ms = time_prefill(engine, make_prompts(("equal", 2048), 1, vocab, seed=99), reps=3)
+            line["prefill_2048_ms"] = round(ms, 3)
+            line["prefill_tokens_per_s"] = round(2048 / (ms / 1e3), 1)
+            for b in (8, 64):
+                r = device_decode(engine, make_prompts(("equal", 512), b, vocab, seed=b), args.steps or 64, 3)
+                line[f"decode_b{b}_ms_per_step"] = round(r["ms_per_step"], 4)
+                line[f"decode_b{b}_tokens_per_s"] = round(r["tokens_per_s"], 1)
+                line[f"decode_b{b}_launches_per_step"] = r["graph"].launches_per_step
+            print(json.dumps(line), flush=True)
+            del lm, engine
+            torch.cuda.empty_cache()
+        print(json.dumps({"compare": size, "kernels": compare_kernels(z, pk), "peaks": pk["source"]}), flush=True)
+    return 0
+
+
 def run_ours(args):
     import torch
     import burn_lm_b200 as blm
@@ -384,6 +540,10 @@ def main():
     ap.add_argument("--only", default=None, choices=["decode", "prefill", "sweep"],
                     help="run one workload briefly (for profilers), or a sweep over batch sizes and context lengths")
     ap.add_argument("--prompt-tokens", type=int, default=0, help="with --only prefill: one prompt of this many tokens instead of the workload's")
+    ap.add_argument("--compare", default=None, choices=["fobilorn"],
+                    help="instead of the workload: the named design beside the dense Llama decoder at equal layer sizes "
+                         "(prefill and decode throughput, then its kernels alone), one JSON line each")
+    ap.add_argument("--size", default=None, choices=sorted(COMPARE_SIZES), help="with --compare: one of the sizes only")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (both numbers are named in config)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -394,6 +554,8 @@ def main():
     if args.gpus != 1:
         print(f"burn-lm_b200 generates on ONE GPU; --gpus {args.gpus} is not built (no multi-GPU path)")
         return 2
+    if args.compare:
+        return run_compare(args)
     return run_ours(args)
 
 

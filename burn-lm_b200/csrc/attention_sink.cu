@@ -97,22 +97,54 @@ BLM_API int blm_qk_norm_append(const float* proj, long long proj_stride, int n_t
 }
 
 // ---------------------------------------------------------------------------------------------
-// The row kernel: one block per (query row, kv head), one warp per query head of the group (in turns when the
-// group has more heads than the block has warps).  The visible keys of the row are walked in chunks of 32: the
-// block stages a chunk's keys and values in shared memory, every lane of a warp scores one key, and the lanes
-// then own the lanes of the output.  It serves prompts and single tokens alike.
+// The row kernel: one block per (query row, kv head, split of the keys), one warp per query head of the group (in
+// turns when the group has more heads than the block has warps).  The visible keys of the row are walked in chunks
+// of 32: the block stages a chunk's keys and values in shared memory (16-byte loads where the sizes allow), every
+// lane of a warp scores one key, and the lanes then own the lanes of the output.  It serves single tokens, short
+// portions, 32-bit prompts and every head size.  With several splits each block leaves (max, sum, unnormalised
+// output) of its share of the keys and attention_sink_combine_kernel puts them together; the sink belongs to split 0.
 // ---------------------------------------------------------------------------------------------
 constexpr int kChunk = 32;
 constexpr int kMaxVRegs = 8;      // value lanes per thread: dv <= 32 * kMaxVRegs
+
+// `count` consecutive elements of a cache row (count a multiple of the vector width where `vec`) to fp32
+template <typename T>
+__device__ __forceinline__ void stage_row(float* dst, const T* src, int d0, bool vec);
+template <>
+__device__ __forceinline__ void stage_row<float>(float* dst, const float* src, int d0, bool vec) {
+    if (vec) {
+        const float4 a = *reinterpret_cast<const float4*>(src + d0), b = *reinterpret_cast<const float4*>(src + d0 + 4);
+        dst[d0] = a.x; dst[d0 + 1] = a.y; dst[d0 + 2] = a.z; dst[d0 + 3] = a.w;
+        dst[d0 + 4] = b.x; dst[d0 + 5] = b.y; dst[d0 + 6] = b.z; dst[d0 + 7] = b.w;
+    } else {
+        dst[d0] = src[d0];
+    }
+}
+template <>
+__device__ __forceinline__ void stage_row<__nv_bfloat16>(float* dst, const __nv_bfloat16* src, int d0, bool vec) {
+    if (vec) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(src + d0);
+        const __nv_bfloat162* pr = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(pr[e]);
+            dst[d0 + 2 * e] = f.x;
+            dst[d0 + 2 * e + 1] = f.y;
+        }
+    } else {
+        dst[d0] = __bfloat162float(src[d0]);
+    }
+}
 
 template <typename T>
 __global__ void attention_sink_rows_kernel(const T* __restrict__ q, const T* __restrict__ pool, long long page_elems,
                                            const int* __restrict__ block_table, int table_stride, const int* __restrict__ token_seq,
                                            const int* __restrict__ token_pos, const int* __restrict__ slot_of_seq,
-                                           const float* __restrict__ gate, long long gate_stride, T* __restrict__ out, int n_heads,
-                                           int n_kv, int dk, int dv, int page_size, int window, int keep_first, float scale, int sink) {
+                                           const float* __restrict__ gate, long long gate_stride, T* __restrict__ out,
+                                           float* __restrict__ partial, int n_heads, int n_kv, int dk, int dv, int page_size,
+                                           int window, int keep_first, float scale, int sink) {
     extern __shared__ float smem[];
-    const int n = blockIdx.x, kvh = blockIdx.y;
+    const int n = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, n_splits = gridDim.z;
     const int group = n_heads / n_kv;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     const int kstride = dk + 1;                        // odd row length: the lanes of a warp read one column of 32 rows
@@ -122,7 +154,13 @@ __global__ void attention_sink_rows_kernel(const T* __restrict__ q, const T* __r
     const int seq = token_seq[n];
     T* orow = out + (size_t)n * n_heads * dv;
     if (seq < 0) {                                     // a row of no sequence: zeros, nothing read
-        for (int c = threadIdx.x; c < group * dv; c += blockDim.x) orow[(size_t)kvh * group * dv + c] = from_f32<T>(0.f);
+        if (split == 0)
+            for (int c = threadIdx.x; c < group * dv; c += blockDim.x) orow[(size_t)kvh * group * dv + c] = from_f32<T>(0.f);
+        if (n_splits > 1)
+            for (int c = threadIdx.x; c < group * (dv + 2); c += blockDim.x) {
+                const int head = kvh * group + c / (dv + 2), e = c % (dv + 2);
+                partial[(((size_t)n * n_heads + head) * n_splits + split) * (dv + 2) + e] = e == 0 ? -INFINITY : 0.f;
+            }
         return;
     }
     const int pos = token_pos[n];
@@ -130,56 +168,59 @@ __global__ void attention_sink_rows_kernel(const T* __restrict__ q, const T* __r
     const int lo = max(0, pos - window + 1);           // first key of the window
     const int n_first = min(keep_first, lo);           // kept first keys that lie before the window
     const int total = n_first + (pos - lo + 1);
+    const int n_chunks = (total + kChunk - 1) / kChunk;
+    const int per_split = (n_chunks + n_splits - 1) / n_splits;
+    const int c_begin = split * per_split * kChunk, c_end = min(total, (split + 1) * per_split * kChunk);
+    const bool kvec = (dk % 8) == 0, vvec = (dv % 8) == 0;       // rows start on 16-byte borders then (pages do always)
+    const int kstep = kvec ? 8 : 1, vstep = vvec ? 8 : 1;
+    const bool with_sink = sink && split == 0;
     for (int h0 = 0; h0 < group; h0 += n_warps) {
         const int head = kvh * group + h0 + warp;
         const bool active = h0 + warp < group;
         __syncthreads();                               // the chunk buffers and qs of the heads before are done with
         if (active)
             for (int d = lane; d < dk; d += 32) qs[warp * dk + d] = to_f32(q[((size_t)n * n_heads + head) * dk + d]);
-        float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;
+        float m = with_sink ? 0.f : -INFINITY, l = with_sink ? 1.f : 0.f;
         float acc[kMaxVRegs];
 #pragma unroll
         for (int i = 0; i < kMaxVRegs; ++i) acc[i] = 0.f;
-        for (int c0 = 0; c0 < total; c0 += kChunk) {
+        for (int c0 = c_begin; c0 < c_end; c0 += kChunk) {
             __syncthreads();
-            for (int idx = threadIdx.x; idx < kChunk * dk; idx += blockDim.x) {
-                const int row = idx / dk, d = idx % dk, i = c0 + row;
-                float v = 0.f;
-                if (i < total) {
+            for (int idx = threadIdx.x; idx < kChunk * (dk / kstep); idx += blockDim.x) {
+                const int row = idx / (dk / kstep), d = (idx % (dk / kstep)) * kstep, i = c0 + row;
+                if (i < c_end) {
                     const int j = i < n_first ? i : lo + (i - n_first);
                     const T* kpage = pool + (size_t)pages[j / page_size] * page_elems;
-                    v = to_f32(kpage[((size_t)kvh * page_size + j % page_size) * dk + d]);
+                    stage_row<T>(ks + row * kstride, kpage + ((size_t)kvh * page_size + j % page_size) * dk, d, kvec);
                 }
-                ks[row * kstride + d] = v;
             }
-            for (int idx = threadIdx.x; idx < kChunk * dv; idx += blockDim.x) {
-                const int row = idx / dv, d = idx % dv, i = c0 + row;
-                float v = 0.f;
-                if (i < total) {
+            for (int idx = threadIdx.x; idx < kChunk * (dv / vstep); idx += blockDim.x) {
+                const int row = idx / (dv / vstep), d = (idx % (dv / vstep)) * vstep, i = c0 + row;
+                if (i < c_end) {
                     const int j = i < n_first ? i : lo + (i - n_first);
                     const T* vpage = pool + (size_t)pages[j / page_size] * page_elems + (size_t)n_kv * page_size * dk;
-                    v = to_f32(vpage[((size_t)kvh * page_size + j % page_size) * dv + d]);
+                    stage_row<T>(vs + row * dv, vpage + ((size_t)kvh * page_size + j % page_size) * dv, d, vvec);
                 }
-                vs[row * dv + d] = v;
             }
             __syncthreads();
             if (active) {
+                const bool mine = c0 + lane < c_end;
                 float s = -INFINITY;
-                if (c0 + lane < total) {
+                if (mine) {
                     float dot = 0.f;
                     const float* kr = ks + lane * kstride;
                     const float* qr = qs + warp * dk;
                     for (int d = 0; d < dk; ++d) dot = fmaf(qr[d], kr[d], dot);
                     s = dot * scale;
                 }
-                const float m_new = fmaxf(m, warp_max(s));
-                const float p = (c0 + lane < total) ? expf(s - m_new) : 0.f;
-                const float corr = expf(m - m_new);          // m = -inf only before the first chunk, where m_new is finite
+                const float m_new = fmaxf(m, warp_max(s));      // finite: the chunk has a key
+                const float p = mine ? expf(s - m_new) : 0.f;
+                const float corr = expf(m - m_new);             // m = -inf only before the first chunk
                 l = l * corr + warp_sum(p);
                 m = m_new;
 #pragma unroll
                 for (int i = 0; i < kMaxVRegs; ++i) acc[i] *= corr;
-                const int rows = min(kChunk, total - c0);
+                const int rows = min(kChunk, c_end - c0);
                 for (int j = 0; j < rows; ++j) {
                     const float pj = __shfl_sync(0xffffffffu, p, j);
 #pragma unroll
@@ -190,7 +231,18 @@ __global__ void attention_sink_rows_kernel(const T* __restrict__ q, const T* __r
                 }
             }
         }
-        if (active) {
+        if (active && n_splits > 1) {
+            float* part = partial + (((size_t)n * n_heads + head) * n_splits + split) * (dv + 2);
+            if (lane == 0) {
+                part[0] = m;
+                part[1] = l;
+            }
+#pragma unroll
+            for (int i = 0; i < kMaxVRegs; ++i) {
+                const int d = lane + 32 * i;
+                if (d < dv) part[2 + d] = acc[i];
+            }
+        } else if (active) {
             float g = 1.f;
             if (gate != nullptr) g = 1.0f / (1.0f + expf(-gate[(size_t)n * gate_stride + head]));
             const float inv = l > 0.f ? g / l : 0.f;
@@ -203,11 +255,39 @@ __global__ void attention_sink_rows_kernel(const T* __restrict__ q, const T* __r
     }
 }
 
+// out[n, head] = gate * sum_z acc_z e^(m_z - M) / sum_z l_z e^(m_z - M),  M = max_z m_z: one warp per (row, head)
+template <typename T>
+__global__ void attention_sink_combine_kernel(const float* __restrict__ partial, const float* __restrict__ gate, long long gate_stride,
+                                              T* __restrict__ out, int n_rows, int n_heads, int dv, int n_splits) {
+    const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (item >= n_rows * n_heads) return;
+    const int n = item / n_heads, head = item % n_heads;
+    const float* part = partial + (size_t)item * n_splits * (dv + 2);
+    float big = -INFINITY;
+    for (int z = 0; z < n_splits; ++z) big = fmaxf(big, part[(size_t)z * (dv + 2)]);
+    float l = 0.f;
+    for (int z = 0; z < n_splits; ++z) {
+        const float mz = part[(size_t)z * (dv + 2)];
+        if (mz > -INFINITY) l += part[(size_t)z * (dv + 2) + 1] * expf(mz - big);
+    }
+    float g = 1.f;
+    if (gate != nullptr) g = 1.0f / (1.0f + expf(-gate[(size_t)n * gate_stride + head]));
+    const float inv = l > 0.f ? g / l : 0.f;
+    for (int d = lane; d < dv; d += 32) {
+        float a = 0.f;
+        for (int z = 0; z < n_splits; ++z) {
+            const float mz = part[(size_t)z * (dv + 2)];
+            if (mz > -INFINITY) a += part[(size_t)z * (dv + 2) + 2 + d] * expf(mz - big);
+        }
+        out[((size_t)n * n_heads + head) * dv + d] = from_f32<T>(a * inv);
+    }
+}
+
 template <typename T>
 static int launch_rows(const void* q, const void* pool, long long page_elems, const int* block_table, int table_stride,
                        const int* token_seq, const int* token_pos, const int* slot_of_seq, const float* gate, long long gate_stride,
-                       void* out, int n_tokens, int n_heads, int n_kv, int dk, int dv, int page_size, int window, int keep_first,
-                       float scale, int sink, cudaStream_t stream) {
+                       void* out, float* partial, int n_splits, int n_tokens, int n_heads, int n_kv, int dk, int dv, int page_size,
+                       int window, int keep_first, float scale, int sink, cudaStream_t stream) {
     const int group = n_heads / n_kv;
     const int warps = group < 8 ? group : 8;
     const size_t smem = ((size_t)kChunk * (dk + 1) + (size_t)kChunk * dv + (size_t)warps * dk) * sizeof(float);
@@ -216,29 +296,526 @@ static int launch_rows(const void* q, const void* pool, long long page_elems, co
         cudaError_t e = cudaFuncSetAttribute(attention_sink_rows_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "attention_sink: %s", cudaGetErrorString(e));
     }
-    attention_sink_rows_kernel<T><<<dim3(n_tokens, n_kv), warps * 32, smem, stream>>>(
+    attention_sink_rows_kernel<T><<<dim3(n_tokens, n_kv, n_splits), warps * 32, smem, stream>>>(
         (const T*)q, (const T*)pool, page_elems, block_table, table_stride, token_seq, token_pos, slot_of_seq, gate, gate_stride,
-        (T*)out, n_heads, n_kv, dk, dv, page_size, window, keep_first, scale, sink);
+        (T*)out, partial, n_heads, n_kv, dk, dv, page_size, window, keep_first, scale, sink);
+    if (n_splits > 1) {
+        const int items = n_tokens * n_heads;
+        attention_sink_combine_kernel<T><<<(items + 3) / 4, 128, 0, stream>>>(partial, gate, gate_stride, (T*)out, n_tokens, n_heads, dv,
+                                                                              n_splits);
+    }
     return blm_check_launch("attention_sink");
+}
+
+// ---------------------------------------------------------------------------------------------
+// The tensor-core kernels (bfloat16, mma.sync m16n8k16 with fp32 sums, operands fetched with ldmatrix).  Keys and
+// values come a cache page (64 positions) at a time through cp.async into two buffers in turn, so that the next page
+// is on its way while this one is worked on: first the pages of the kept first tokens that lie wholly before the
+// window, then the pages from the window's start to the last query.  Keys that a query must not see are masked by
+// position; the values of keys beyond the last query are staged as zeros, so that what a page's unused rows hold
+// never meets the sums.  NV: value lanes in tiles of 8 (dv <= 8 NV); dk and dv are multiples of 8.
+//
+// Prompt kernel: a block of four warps per (64 query rows of one sequence, query head); a warp owns 16 query rows, so
+// a row's softmax stays inside a quad of lanes.
+// Decode kernel: a block per (token, kv head, split of the pages); the rows of the tile are the query heads of the
+// group (up to 16), and each warp takes 16 of a page's 64 keys with a running softmax of its own; the four are put
+// together at the end.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+// four 8x8 tiles of 16-bit elements: lanes 8i .. 8i + 7 give the addresses of the rows of tile i; a lane receives, of
+// every tile, the elements (lane / 4, 2 (lane % 4)) and the next (transposed: (2 (lane % 4), lane / 4) and the one below)
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const __nv_bfloat16* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const __nv_bfloat16* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+// 16 bytes from global to shared memory without passing registers; `valid` false: zeros instead (nothing is read)
+__device__ __forceinline__ void cp_async16(__nv_bfloat16* dst, const __nv_bfloat16* src, bool valid) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all_but_one() { asm volatile("cp.async.wait_group 1;\n" ::: "memory"); }
+
+constexpr int kTileQ = 64, kTileK = 64;
+
+// The pages a query tile walks: `kept` pages from the sequence's start, then pages wp0 .. wp1.
+struct PageWalk {
+    int kept, wp0, n_tiles;
+    __device__ __forceinline__ PageWalk(int p_first, int p_last, int window, int keep_first) {
+        const int lo = max(0, p_first - window + 1);
+        wp0 = lo / kTileK;
+        kept = min((keep_first + kTileK - 1) / kTileK, wp0);
+        n_tiles = kept + (p_last / kTileK - wp0 + 1);
+    }
+    __device__ __forceinline__ int page(int it) const { return it < kept ? it : wp0 + (it - kept); }
+};
+
+// one page's keys and values of one kv head into a buffer pair (every thread of the block takes its share)
+__device__ __forceinline__ void stage_page(__nv_bfloat16* kbuf, __nv_bfloat16* vbuf, const __nv_bfloat16* page, int n_kv, int kvh, int dk,
+                                           int dv, int qstride, int vstride, int first_pos, int p_last) {
+    const __nv_bfloat16* kpage = page + (size_t)kvh * kTileK * dk;
+    const __nv_bfloat16* vpage = page + (size_t)n_kv * kTileK * dk + (size_t)kvh * kTileK * dv;
+    const int kvec = dk / 8, vvec = dv / 8;
+    for (int idx = threadIdx.x; idx < kTileK * kvec; idx += blockDim.x) {
+        const int r = idx / kvec, c = (idx % kvec) * 8;
+        cp_async16(kbuf + r * qstride + c, kpage + (size_t)r * dk + c, true);
+    }
+    for (int idx = threadIdx.x; idx < kTileK * vvec; idx += blockDim.x) {
+        const int r = idx / vvec, c = (idx % vvec) * 8;
+        cp_async16(vbuf + r * vstride + c, vpage + (size_t)r * dv + c, first_pos + r <= p_last);
+    }
+}
+
+template <int NV>
+__global__ void __launch_bounds__(128) attention_sink_prompt_kernel(
+    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pool, long long page_elems,
+    const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ start_pos,
+    const int* __restrict__ slot_of_seq, int n_seqs, int n_tokens, const float* __restrict__ gate, long long gate_stride,
+    __nv_bfloat16* __restrict__ out, int n_heads, int n_kv, int dk, int dv, int window, int keep_first, float scale, int sink) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __shared__ int found[3];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int dkp = (dk + 15) & ~15;                   // the reduction runs in steps of 16 lanes; the rest is zeros
+    const int qstride = dkp + 8;                       // rows 16 bytes apart modulo 128: ldmatrix reads eight of them at once
+    constexpr int vstride = 8 * NV + 8;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [64][qstride]
+    __nv_bfloat16* Kb = Qs + kTileQ * qstride;                           // 2 x [64][qstride]
+    __nv_bfloat16* Vb = Kb + 2 * kTileK * qstride;                       // 2 x [64][vstride]
+    const int head = blockIdx.y;
+    if (tid == 0) {
+        int t = blockIdx.x;
+        found[0] = -1;
+        for (int s = 0; s < n_seqs; ++s) {
+            const int len = cu_seqlens[s + 1] - cu_seqlens[s];
+            const int tiles = (len + kTileQ - 1) / kTileQ;
+            if (t < tiles) {
+                found[0] = s;
+                found[1] = t * kTileQ;
+                found[2] = len;
+                break;
+            }
+            t -= tiles;
+        }
+    }
+    __syncthreads();
+    if (found[0] < 0) {
+        // a block without a tile: the rows after the last sequence (padding up to a captured step's size) get zeros
+        const int end = cu_seqlens[n_seqs];
+        for (int idx = tid; idx < (n_tokens - end) * dv; idx += blockDim.x)
+            out[((size_t)(end + idx / dv) * n_heads + head) * dv + idx % dv] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    const int seq = found[0], t0 = found[1], len = found[2];
+    const int kvh = head / (n_heads / n_kv);
+    const int row0 = cu_seqlens[seq] + t0;             // the tile's first token row
+    const int rows = min(kTileQ, len - t0);
+    const int p0 = start_pos[seq] + t0;                // its position
+    const int p_last = p0 + rows - 1;
+    const int* pages = block_table + (size_t)slot_of_seq[seq] * table_stride;
+    {   // zeros everywhere first: rows of no query, lanes beyond dk and dv
+        const int total = (3 * kTileQ * qstride + 2 * kTileK * vstride) / 8;
+        for (int idx = tid; idx < total; idx += 128) reinterpret_cast<uint4*>(smem_raw)[idx] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    __syncthreads();
+    const PageWalk walk(p0, p_last, window, keep_first);
+    for (int idx = tid; idx < rows * (dk / 8); idx += 128) {
+        const int r = idx / (dk / 8), c = (idx % (dk / 8)) * 8;
+        cp_async16(Qs + r * qstride + c, q + ((size_t)(row0 + r) * n_heads + head) * dk + c, true);
+    }
+    stage_page(Kb, Vb, pool + (size_t)pages[walk.page(0)] * page_elems, n_kv, kvh, dk, dv, qstride, vstride, walk.page(0) * kTileK, p_last);
+    cp_async_commit();
+    const int quad = lane >> 2, pair = (lane & 3) * 2;
+    const int lrow = lane & 7, lmat = lane >> 3;
+    const int pr0 = p0 + warp * 16 + quad, pr1 = pr0 + 8;        // positions of this thread's two rows
+    float m[2], l[2], o[NV][4];
+    m[0] = m[1] = sink ? 0.f : -INFINITY;
+    l[0] = l[1] = sink ? 0.25f : 0.f;                  // a quad's four lanes add up to the sink's one
+#pragma unroll
+    for (int j = 0; j < NV; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    const __nv_bfloat16* qa = Qs + (warp * 16 + lrow + (lmat & 1) * 8) * qstride + (lmat >> 1) * 8;
+    for (int it = 0; it < walk.n_tiles; ++it) {
+        const int buf = it & 1;
+        if (it + 1 < walk.n_tiles) {
+            const int pg = walk.page(it + 1);
+            stage_page(Kb + (buf ^ 1) * kTileK * qstride, Vb + (buf ^ 1) * kTileK * vstride, pool + (size_t)pages[pg] * page_elems, n_kv, kvh,
+                       dk, dv, qstride, vstride, pg * kTileK, p_last);
+        }
+        cp_async_commit();
+        cp_async_wait_all_but_one();                   // this tile (and the queries) have landed; the next may be on its way
+        __syncthreads();
+        const int pg = walk.page(it);
+        const __nv_bfloat16* kb = Kb + buf * kTileK * qstride + (lrow + (lmat >> 1) * 8) * qstride + (lmat & 1) * 8;
+        const __nv_bfloat16* vb = Vb + buf * kTileK * vstride + (lrow + (lmat & 1) * 8) * vstride + (lmat >> 1) * 8;
+        float s[8][4];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+        for (int kk = 0; kk < dkp; kk += 16) {
+            uint32_t a[4], b[4];
+            ldsm_x4(a, qa + kk);
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+                ldsm_x4(b, kb + 16 * jj * qstride + kk);
+                mma_bf16(s[2 * jj], a, b[0], b[1]);
+                mma_bf16(s[2 * jj + 1], a, b[2], b[3]);
+            }
+        }
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = pg * kTileK + 8 * j + pair + (e & 1);
+                const int pr = e < 2 ? pr0 : pr1;
+                const bool sees = key <= pr && (pr - key < window || key < keep_first);
+                const float v = sees ? s[j][e] * scale : -INFINITY;
+                s[j][e] = v;
+                if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+            }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
+        const float use0 = mn0 == -INFINITY ? 0.f : mn0, use1 = mn1 == -INFINITY ? 0.f : mn1;    // a row that has seen no key yet
+        const float corr0 = expf(m[0] - use0), corr1 = expf(m[1] - use1);
+        m[0] = mn0;
+        m[1] = mn1;
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            s[j][0] = expf(s[j][0] - use0); s[j][1] = expf(s[j][1] - use0);
+            s[j][2] = expf(s[j][2] - use1); s[j][3] = expf(s[j][3] - use1);
+            sum0 += s[j][0] + s[j][1];
+            sum1 += s[j][2] + s[j][3];
+        }
+        l[0] = l[0] * corr0 + sum0;
+        l[1] = l[1] * corr1 + sum1;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            o[j][0] *= corr0; o[j][1] *= corr0;
+            o[j][2] *= corr1; o[j][3] *= corr1;
+        }
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {               // 16 keys a step: two of the score tiles make one operand
+            uint32_t a[4], b[4];
+            a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]); a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+            a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]); a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int jj = 0; jj < NV / 2; ++jj) {
+                ldsm_x4_trans(b, vb + 16 * kk * vstride + 16 * jj);
+                mma_bf16(o[2 * jj], a, b[0], b[1]);
+                mma_bf16(o[2 * jj + 1], a, b[2], b[3]);
+            }
+        }
+        __syncthreads();                               // the buffer may be filled again
+    }
+    l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1);
+    l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
+    l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1);
+    l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
+    const int r0 = warp * 16 + quad, r1 = r0 + 8;
+    float inv0 = 0.f, inv1 = 0.f;
+    if (r0 < rows) {
+        const float g = gate ? 1.0f / (1.0f + expf(-gate[(size_t)(row0 + r0) * gate_stride + head])) : 1.f;
+        inv0 = l[0] > 0.f ? g / l[0] : 0.f;
+    }
+    if (r1 < rows) {
+        const float g = gate ? 1.0f / (1.0f + expf(-gate[(size_t)(row0 + r1) * gate_stride + head])) : 1.f;
+        inv1 = l[1] > 0.f ? g / l[1] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const int d = 8 * j + pair;
+        if (d < dv) {
+            if (r0 < rows)
+                *reinterpret_cast<uint32_t*>(out + ((size_t)(row0 + r0) * n_heads + head) * dv + d) = pack_bf16(o[j][0] * inv0, o[j][1] * inv0);
+            if (r1 < rows)
+                *reinterpret_cast<uint32_t*>(out + ((size_t)(row0 + r1) * n_heads + head) * dv + d) = pack_bf16(o[j][2] * inv1, o[j][3] * inv1);
+        }
+    }
+}
+
+template <int NV>
+static int launch_prompt(const void* q, const void* pool, long long page_elems, const int* block_table, int table_stride,
+                         const int* cu_seqlens, const int* start_pos, const int* slot_of_seq, int n_seqs, const float* gate,
+                         long long gate_stride, void* out, int n_tokens, int n_heads, int n_kv, int dk, int dv, int window,
+                         int keep_first, float scale, int sink, cudaStream_t stream) {
+    const int dkp = (dk + 15) & ~15;
+    const size_t smem = ((size_t)3 * kTileQ * (dkp + 8) + (size_t)2 * kTileK * (8 * NV + 8)) * sizeof(__nv_bfloat16);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(attention_sink_prompt_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "attention_sink: %s", cudaGetErrorString(e));
+    }
+    const unsigned tiles = (unsigned)((n_tokens + kTileQ - 1) / kTileQ + n_seqs);     // every sequence may end in a tile that is not full
+    attention_sink_prompt_kernel<NV><<<dim3(tiles, n_heads), 128, smem, stream>>>(
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)pool, page_elems, block_table, table_stride, cu_seqlens, start_pos, slot_of_seq,
+        n_seqs, n_tokens, gate, gate_stride, (__nv_bfloat16*)out, n_heads, n_kv, dk, dv, window, keep_first, scale, sink);
+    return blm_check_launch("attention_sink (prompt)");
+}
+
+template <int NV>
+__global__ void __launch_bounds__(128) attention_sink_decode_kernel(
+    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pool, long long page_elems,
+    const int* __restrict__ block_table, int table_stride, const int* __restrict__ token_seq, const int* __restrict__ token_pos,
+    const int* __restrict__ slot_of_seq, const float* __restrict__ gate, long long gate_stride, __nv_bfloat16* __restrict__ out,
+    float* __restrict__ partial, int n_heads, int n_kv, int dk, int dv, int window, int keep_first, float scale, int sink) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, n_splits = gridDim.z;
+    const int group = n_heads / n_kv;                  // <= 16: the rows of the tile
+    const int dkp = (dk + 15) & ~15;
+    const int qstride = dkp + 8;
+    constexpr int vstride = 8 * NV + 8;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [16][qstride]
+    __nv_bfloat16* Kb = Qs + 16 * qstride;                               // 2 x [64][qstride]
+    __nv_bfloat16* Vb = Kb + 2 * kTileK * qstride;                       // 2 x [64][vstride]
+    const int seq = token_seq[n];
+    const int head0 = kvh * group;
+    if (seq < 0) {                                     // a row of no sequence: zeros, nothing read
+        if (split == 0)
+            for (int c = tid; c < group * dv; c += 128) out[((size_t)n * n_heads + head0) * dv + c] = __float2bfloat16_rn(0.f);
+        if (n_splits > 1)
+            for (int c = tid; c < group * (dv + 2); c += 128) {
+                const int head = head0 + c / (dv + 2), e = c % (dv + 2);
+                partial[(((size_t)n * n_heads + head) * n_splits + split) * (dv + 2) + e] = e == 0 ? -INFINITY : 0.f;
+            }
+        return;
+    }
+    const int pos = token_pos[n];
+    const int* pages = block_table + (size_t)slot_of_seq[seq] * table_stride;
+    {
+        const int total = (16 * qstride + 2 * kTileK * qstride + 2 * kTileK * vstride) / 8;
+        for (int idx = tid; idx < total; idx += 128) reinterpret_cast<uint4*>(smem_raw)[idx] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    __syncthreads();
+    const PageWalk walk(pos, pos, window, keep_first);
+    const int per_split = (walk.n_tiles + n_splits - 1) / n_splits;
+    const int it_begin = split * per_split, it_end = min(walk.n_tiles, it_begin + per_split);
+    for (int idx = tid; idx < group * (dk / 8); idx += 128) {
+        const int r = idx / (dk / 8), c = (idx % (dk / 8)) * 8;
+        cp_async16(Qs + r * qstride + c, q + ((size_t)n * n_heads + head0 + r) * dk + c, true);
+    }
+    if (it_begin < it_end)
+        stage_page(Kb, Vb, pool + (size_t)pages[walk.page(it_begin)] * page_elems, n_kv, kvh, dk, dv, qstride, vstride,
+                   walk.page(it_begin) * kTileK, pos);
+    cp_async_commit();
+    const int quad = lane >> 2, pair = (lane & 3) * 2;
+    const int lrow = lane & 7, lmat = lane >> 3;
+    const bool with_sink = sink && split == 0 && warp == 0;      // the sink is counted once
+    float m[2], l[2], o[NV][4];
+    m[0] = m[1] = with_sink ? 0.f : -INFINITY;
+    l[0] = l[1] = with_sink ? 0.25f : 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    const __nv_bfloat16* qa = Qs + (lrow + (lmat & 1) * 8) * qstride + (lmat >> 1) * 8;
+    for (int it = it_begin; it < it_end; ++it) {
+        const int buf = (it - it_begin) & 1;
+        if (it + 1 < it_end) {
+            const int pg = walk.page(it + 1);
+            stage_page(Kb + (buf ^ 1) * kTileK * qstride, Vb + (buf ^ 1) * kTileK * vstride, pool + (size_t)pages[pg] * page_elems, n_kv, kvh,
+                       dk, dv, qstride, vstride, pg * kTileK, pos);
+        }
+        cp_async_commit();
+        cp_async_wait_all_but_one();
+        __syncthreads();
+        const int pg = walk.page(it);
+        // this warp's 16 keys of the page
+        const __nv_bfloat16* kb = Kb + buf * kTileK * qstride + (16 * warp + lrow + (lmat >> 1) * 8) * qstride + (lmat & 1) * 8;
+        const __nv_bfloat16* vb = Vb + buf * kTileK * vstride + (16 * warp + lrow + (lmat & 1) * 8) * vstride + (lmat >> 1) * 8;
+        float s[2][4];
+        s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
+        for (int kk = 0; kk < dkp; kk += 16) {
+            uint32_t a[4], b[4];
+            ldsm_x4(a, qa + kk);
+            ldsm_x4(b, kb + kk);
+            mma_bf16(s[0], a, b[0], b[1]);
+            mma_bf16(s[1], a, b[2], b[3]);
+        }
+        float mx = -INFINITY;                          // every row (head) sees the same keys
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = pg * kTileK + 16 * warp + 8 * j + pair + (e & 1);
+                const bool sees = key <= pos && (pos - key < window || key < keep_first);
+                s[j][e] = sees ? s[j][e] * scale : -INFINITY;
+            }
+        float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+        float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        (void)mx;
+        const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
+        const float use0 = mn0 == -INFINITY ? 0.f : mn0, use1 = mn1 == -INFINITY ? 0.f : mn1;
+        const float corr0 = expf(m[0] - use0), corr1 = expf(m[1] - use1);
+        m[0] = mn0;
+        m[1] = mn1;
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            s[j][0] = expf(s[j][0] - use0); s[j][1] = expf(s[j][1] - use0);
+            s[j][2] = expf(s[j][2] - use1); s[j][3] = expf(s[j][3] - use1);
+            sum0 += s[j][0] + s[j][1];
+            sum1 += s[j][2] + s[j][3];
+        }
+        l[0] = l[0] * corr0 + sum0;
+        l[1] = l[1] * corr1 + sum1;
+        uint32_t a[4], b[4];
+        a[0] = pack_bf16(s[0][0], s[0][1]); a[1] = pack_bf16(s[0][2], s[0][3]);
+        a[2] = pack_bf16(s[1][0], s[1][1]); a[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+        for (int jj = 0; jj < NV / 2; ++jj) {
+            o[2 * jj][0] *= corr0; o[2 * jj][1] *= corr0; o[2 * jj][2] *= corr1; o[2 * jj][3] *= corr1;
+            o[2 * jj + 1][0] *= corr0; o[2 * jj + 1][1] *= corr0; o[2 * jj + 1][2] *= corr1; o[2 * jj + 1][3] *= corr1;
+            ldsm_x4_trans(b, vb + 16 * jj);
+            mma_bf16(o[2 * jj], a, b[0], b[1]);
+            mma_bf16(o[2 * jj + 1], a, b[2], b[3]);
+        }
+        __syncthreads();
+    }
+    // the four warps' shares of the keys are put together through shared memory: [warp][row][max, sum, dv lanes]
+    l[0] += __shfl_xor_sync(0xffffffffu, l[0], 1);
+    l[0] += __shfl_xor_sync(0xffffffffu, l[0], 2);
+    l[1] += __shfl_xor_sync(0xffffffffu, l[1], 1);
+    l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
+    float* sh = reinterpret_cast<float*>(Kb);          // the page buffers are done with (the loop ended on a barrier)
+    const int rstride = 8 * NV + 2;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = quad + 8 * half;
+        float* dst = sh + ((size_t)warp * 16 + r) * rstride;
+        if (pair == 0) {
+            dst[0] = m[half];
+            dst[1] = l[half];
+        }
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            dst[2 + 8 * j + pair] = o[j][2 * half];
+            dst[2 + 8 * j + pair + 1] = o[j][2 * half + 1];
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < group * dv; idx += 128) {
+        const int r = idx / dv, d = idx % dv;
+        float big = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) big = fmaxf(big, sh[((size_t)w * 16 + r) * rstride]);
+        float lsum = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float* src = sh + ((size_t)w * 16 + r) * rstride;
+            if (src[0] > -INFINITY) {
+                const float f = expf(src[0] - big);
+                lsum += src[1] * f;
+                acc += src[2 + d] * f;
+            }
+        }
+        const int head = head0 + r;
+        if (n_splits > 1) {
+            float* part = partial + (((size_t)n * n_heads + head) * n_splits + split) * (dv + 2);
+            if (d == 0) {
+                part[0] = big;
+                part[1] = lsum;
+            }
+            part[2 + d] = acc;
+        } else {
+            const float g = gate ? 1.0f / (1.0f + expf(-gate[(size_t)n * gate_stride + head])) : 1.f;
+            out[((size_t)n * n_heads + head) * dv + d] = __float2bfloat16_rn(lsum > 0.f ? acc * g / lsum : 0.f);
+        }
+    }
+}
+
+template <int NV>
+static int launch_decode(const void* q, const void* pool, long long page_elems, const int* block_table, int table_stride,
+                         const int* token_seq, const int* token_pos, const int* slot_of_seq, const float* gate, long long gate_stride,
+                         void* out, float* partial, int n_splits, int n_tokens, int n_heads, int n_kv, int dk, int dv, int window,
+                         int keep_first, float scale, int sink, cudaStream_t stream) {
+    const int dkp = (dk + 15) & ~15;
+    size_t smem = ((size_t)16 * (dkp + 8) + (size_t)2 * kTileK * (dkp + 8) + (size_t)2 * kTileK * (8 * NV + 8)) * sizeof(__nv_bfloat16);
+    const size_t merge = (size_t)16 * (dkp + 8) * sizeof(__nv_bfloat16) + (size_t)4 * 16 * (8 * NV + 2) * sizeof(float);
+    if (merge > smem) smem = merge;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(attention_sink_decode_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "attention_sink: %s", cudaGetErrorString(e));
+    }
+    attention_sink_decode_kernel<NV><<<dim3(n_tokens, n_kv, n_splits), 128, smem, stream>>>(
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)pool, page_elems, block_table, table_stride, token_seq, token_pos, slot_of_seq, gate,
+        gate_stride, (__nv_bfloat16*)out, partial, n_heads, n_kv, dk, dv, window, keep_first, scale, sink);
+    if (n_splits > 1) {
+        const int items = n_tokens * n_heads;
+        attention_sink_combine_kernel<__nv_bfloat16><<<(items + 3) / 4, 128, 0, stream>>>(partial, gate, gate_stride, (__nv_bfloat16*)out,
+                                                                                         n_tokens, n_heads, dv, n_splits);
+    }
+    return blm_check_launch("attention_sink (decode)");
+}
+
+// Whether a step of this shape runs the prompt kernel (else the row kernel): bfloat16, pages of 64, sizes it takes,
+// and portions long enough to fill some of a tile's rows.
+BLM_API int blm_attention_sink_prompt_takes(int dtype, int dk, int dv, int page_size, int max_q_len, int n_heads) {
+    return dtype == BLM_BF16 && page_size == kTileK && dk % 8 == 0 && dv % 8 == 0 && dk >= 8 && dk <= 256 && dv >= 8 && dv <= 128 &&
+           max_q_len >= 8 && n_heads <= 65535;
+}
+
+// Whether single tokens and short portions of this shape run the tensor-core decode kernel (else the row kernel): the
+// same sizes, and a group of query heads that fits the 16 rows of a tile.  The keys are then cut by pages: a split
+// should have a page at least.
+BLM_API int blm_attention_sink_decode_takes(int dtype, int dk, int dv, int page_size, int n_heads, int n_kv) {
+    return dtype == BLM_BF16 && page_size == kTileK && dk % 8 == 0 && dv % 8 == 0 && dk >= 8 && dk <= 256 && dv >= 8 && dv <= 128 &&
+           n_kv > 0 && n_heads % n_kv == 0 && n_heads / n_kv <= 16;
 }
 
 BLM_API int blm_attention_sink(const void* q, const void* pool, int dtype, long long page_elems, const int* block_table,
                                int table_stride, const int* token_seq, const int* token_pos, const int* slot_of_seq,
-                               const float* gate, long long gate_stride, void* out, int n_tokens, int n_heads, int n_kv, int dk,
-                               int dv, int page_size, int window, int keep_first, float scale, int sink, cudaStream_t stream) {
+                               const int* cu_seqlens, const int* start_pos, int n_seqs, int max_q_len, const float* gate,
+                               long long gate_stride, void* out, float* partial, int n_splits, int n_tokens, int n_heads, int n_kv,
+                               int dk, int dv, int page_size, int window, int keep_first, float scale, int sink, cudaStream_t stream) {
     if (n_tokens == 0) return BLM_OK;
     BLM_REQUIRE(n_tokens > 0 && n_heads > 0 && n_kv > 0 && n_heads % n_kv == 0 && dk > 0 && dv > 0 && page_size > 0,
                 "attention_sink: bad sizes");
     BLM_REQUIRE(dv <= 32 * kMaxVRegs, "attention_sink: values of %d lanes; at most %d", dv, 32 * kMaxVRegs);
     BLM_REQUIRE(window >= 1 && keep_first >= 0, "attention_sink: window %d, kept first %d", window, keep_first);
     BLM_REQUIRE(page_elems == (long long)n_kv * page_size * (dk + dv), "attention_sink: a page holds n_kv * page * (dk + dv) elements");
-    BLM_REQUIRE(n_kv <= 65535, "attention_sink: %d kv heads", n_kv);
+    BLM_REQUIRE(n_kv <= 65535 && n_splits >= 1 && n_splits <= 65535, "attention_sink: %d kv heads, %d splits", n_kv, n_splits);
+    BLM_REQUIRE(n_splits == 1 || partial != nullptr, "attention_sink: %d splits need scratch", n_splits);
+    if (cu_seqlens != nullptr && start_pos != nullptr && n_seqs > 0 &&
+        blm_attention_sink_prompt_takes(dtype, dk, dv, page_size, max_q_len, n_heads)) {
+#define BLM_PROMPT(NV) launch_prompt<NV>(q, pool, page_elems, block_table, table_stride, cu_seqlens, start_pos, slot_of_seq, n_seqs, gate, \
+                                         gate_stride, out, n_tokens, n_heads, n_kv, dk, dv, window, keep_first, scale, sink, stream)
+        if (dv <= 32) return BLM_PROMPT(4);
+        if (dv <= 64) return BLM_PROMPT(8);
+        return BLM_PROMPT(16);
+#undef BLM_PROMPT
+    }
+    if (blm_attention_sink_decode_takes(dtype, dk, dv, page_size, n_heads, n_kv)) {
+#define BLM_DECODE(NV) launch_decode<NV>(q, pool, page_elems, block_table, table_stride, token_seq, token_pos, slot_of_seq, gate, gate_stride, \
+                                         out, partial, n_splits, n_tokens, n_heads, n_kv, dk, dv, window, keep_first, scale, sink, stream)
+        if (dv <= 32) return BLM_DECODE(4);
+        if (dv <= 64) return BLM_DECODE(8);
+        return BLM_DECODE(16);
+#undef BLM_DECODE
+    }
     if (dtype == BLM_F32)
         return launch_rows<float>(q, pool, page_elems, block_table, table_stride, token_seq, token_pos, slot_of_seq, gate, gate_stride,
-                                  out, n_tokens, n_heads, n_kv, dk, dv, page_size, window, keep_first, scale, sink, stream);
+                                  out, partial, n_splits, n_tokens, n_heads, n_kv, dk, dv, page_size, window, keep_first, scale, sink,
+                                  stream);
     if (dtype == BLM_BF16)
         return launch_rows<__nv_bfloat16>(q, pool, page_elems, block_table, table_stride, token_seq, token_pos, slot_of_seq, gate,
-                                          gate_stride, out, n_tokens, n_heads, n_kv, dk, dv, page_size, window, keep_first, scale, sink,
-                                          stream);
+                                          gate_stride, out, partial, n_splits, n_tokens, n_heads, n_kv, dk, dv, page_size, window,
+                                          keep_first, scale, sink, stream);
     return blm_fail(BLM_BAD_ARGUMENT, "attention_sink: dtype %d", dtype);
 }

@@ -30,7 +30,8 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
         float z = 0.f;
         for (int d = lane; d < width; d += 32) z = fmaf(w[d], x[d], z);
         z = warp_sum(z);
-        if (lane == 0) score[e] = 1.0f / (1.0f + expf(-z));
+        // (a row of no sequence may hold anything, a NaN too: its score is 0, so that it still names experts that exist)
+        if (lane == 0) score[e] = z == z ? 1.0f / (1.0f + expf(-z)) : 0.f;
     }
     __syncthreads();
     if (warp == 0) {
@@ -83,7 +84,7 @@ __global__ void moe_group_kernel(const int* __restrict__ ids, int n_pairs, int n
     int* cursor = counts + n_experts;
     for (int e = threadIdx.x; e < n_experts; e += blockDim.x) counts[e] = 0;
     __syncthreads();
-    for (int a = threadIdx.x; a < n_pairs; a += blockDim.x) atomicAdd(&counts[ids[a]], 1);
+    for (int a = threadIdx.x; a < n_pairs; a += blockDim.x) atomicAdd(&counts[min(max(ids[a], 0), n_experts - 1)], 1);
     __syncthreads();
     if (threadIdx.x == 0) {
         int run = 0;
@@ -96,7 +97,7 @@ __global__ void moe_group_kernel(const int* __restrict__ ids, int n_pairs, int n
     }
     __syncthreads();
     for (int a = threadIdx.x; a < n_pairs; a += blockDim.x) {
-        const int place = atomicAdd(&cursor[ids[a]], 1);
+        const int place = atomicAdd(&cursor[min(max(ids[a], 0), n_experts - 1)], 1);
         order[place] = a;
         place_of[a] = place;
     }
@@ -115,17 +116,18 @@ BLM_API int blm_moe_group(const int* ids, int n_pairs, int n_experts, int* offse
 // ---------------------------------------------------------------------------------------------
 constexpr int kBM = 32, kBN = 32, kBK = 32;
 
-__device__ __forceinline__ bool moe_find_tile(const int* __restrict__ offsets, int n_experts, int tile, int* expert, int* first, int* last) {
+__device__ __forceinline__ bool moe_find_tile(const int* __restrict__ offsets, int n_experts, int tile, int* expert, int* first, int* last,
+                                              int tile_rows = kBM) {
     __shared__ int found[3];
     if (threadIdx.x == 0) {
         int t = tile, e = 0;
         found[0] = -1;
         for (; e < n_experts; ++e) {
             const int begin = offsets[e], end = offsets[e + 1];
-            const int tiles = (end - begin + kBM - 1) / kBM;
+            const int tiles = (end - begin + tile_rows - 1) / tile_rows;
             if (t < tiles) {
                 found[0] = e;
-                found[1] = begin + t * kBM;
+                found[1] = begin + t * tile_rows;
                 found[2] = end;
                 break;
             }
@@ -250,6 +252,184 @@ __global__ void moe_down_kernel(const T* __restrict__ act, const int* __restrict
         }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same grouped products on the tensor cores (bfloat16, mma.sync m16n8k16 with fp32 sums, operands fetched with
+// ldmatrix): tiles of 64 places x 64 outputs, the reduction in slices of 64 that come through cp.async into two
+// buffers in turn; four warps, each 16 places of the tile.  Width and inner size are multiples of 8 (16-byte copies).
+// A weight on the expert's input is applied to both products' sums instead, W (s x) = s (W x), in fp32.
+// ---------------------------------------------------------------------------------------------
+constexpr int kTM = 64, kTN = 64, kTK = 64, kTStride = kTK + 8;     // rows 16 bytes apart modulo 128: ldmatrix reads eight at once
+constexpr int kTile = kTM * kTStride;                               // elements of one staged operand
+
+__device__ __forceinline__ void moe_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void moe_ldsm_x4(uint32_t (&r)[4], const __nv_bfloat16* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void moe_cp16(__nv_bfloat16* dst, const __nv_bfloat16* src, bool valid) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    const int bytes = valid ? 16 : 0;                  // zeros where nothing is to be read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void moe_cp_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+__device__ __forceinline__ void moe_cp_wait_all_but_one() { asm volatile("cp.async.wait_group 1;\n" ::: "memory"); }
+
+// rows [c0, c0 + 64) x lanes [k0, k0 + 64) of a weight [n_rows, n_cols] into ws[64][kTStride]; zeros outside
+__device__ __forceinline__ void moe_stage_weight(__nv_bfloat16* ws, const __nv_bfloat16* __restrict__ w, int n_rows, int n_cols, int c0, int k0) {
+    for (int idx = threadIdx.x; idx < kTN * (kTK / 8); idx += blockDim.x) {
+        const int r = idx / (kTK / 8), kk = (idx % (kTK / 8)) * 8;
+        const bool in = c0 + r < n_rows && k0 + kk < n_cols;
+        moe_cp16(ws + r * kTStride + kk, in ? w + (size_t)(c0 + r) * n_cols + k0 + kk : w, in);
+    }
+}
+
+// 16 places x 64 outputs of one warp: acc[j] += x (16 x 64 slice) . w (64 outputs x 64 slice)
+__device__ __forceinline__ void moe_warp_product(float (&acc)[8][4], const __nv_bfloat16* xa, const __nv_bfloat16* wb) {
+#pragma unroll
+    for (int kk = 0; kk < kTK; kk += 16) {
+        uint32_t a[4], b[4];
+        moe_ldsm_x4(a, xa + kk);
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+            moe_ldsm_x4(b, wb + 16 * jj * kTStride + kk);
+            moe_mma(acc[2 * jj], a, b[0], b[1]);
+            moe_mma(acc[2 * jj + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+__global__ void __launch_bounds__(128) moe_gate_up_tc_kernel(const __nv_bfloat16* __restrict__ h, const float* __restrict__ weights,
+                                                             const int* __restrict__ order, const int* __restrict__ offsets,
+                                                             const __nv_bfloat16* __restrict__ w_gu, __nv_bfloat16* __restrict__ act,
+                                                             int width, int ff, int n_experts, int top, int scale_input) {
+    extern __shared__ __align__(16) unsigned char moe_smem[];
+    __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(moe_smem);      // 2 x (x, gate, up)
+    __shared__ int token_of[kTM];
+    __shared__ float scale_of[kTM];
+    int e, first, last;
+    if (!moe_find_tile(offsets, n_experts, blockIdx.x, &e, &first, &last, kTM)) return;
+    const int c0 = blockIdx.y * kTN;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, quad = lane >> 2, pair = (lane & 3) * 2;
+    const int lrow = lane & 7, lmat = lane >> 3;
+    if (threadIdx.x < kTM) {
+        const int place = first + threadIdx.x;
+        int tok = -1;
+        float sc = 1.f;
+        if (place < last) {
+            const int p = order[place];
+            tok = p / top;
+            if (scale_input) sc = weights[p];
+        }
+        token_of[threadIdx.x] = tok;
+        scale_of[threadIdx.x] = sc;
+    }
+    __syncthreads();
+    const __nv_bfloat16* wg = w_gu + (size_t)e * 2 * ff * width;
+    const __nv_bfloat16* wu = wg + (size_t)ff * width;
+    auto stage_slice = [&](int buf, int k0) {
+        __nv_bfloat16* xs = stage + buf * 3 * kTile;
+        for (int idx = threadIdx.x; idx < kTM * (kTK / 8); idx += blockDim.x) {
+            const int r = idx / (kTK / 8), kk = (idx % (kTK / 8)) * 8;
+            const int tok = token_of[r];
+            const bool in = tok >= 0 && k0 + kk < width;
+            moe_cp16(xs + r * kTStride + kk, in ? h + (size_t)tok * width + k0 + kk : h, in);
+        }
+        moe_stage_weight(xs + kTile, wg, ff, width, c0, k0);
+        moe_stage_weight(xs + 2 * kTile, wu, ff, width, c0, k0);
+    };
+    float g[8][4], u[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) g[j][0] = g[j][1] = g[j][2] = g[j][3] = u[j][0] = u[j][1] = u[j][2] = u[j][3] = 0.f;
+    const int a_off = (warp * 16 + lrow + (lmat & 1) * 8) * kTStride + (lmat >> 1) * 8;
+    const int b_off = (lrow + (lmat >> 1) * 8) * kTStride + (lmat & 1) * 8;
+    stage_slice(0, 0);
+    moe_cp_commit();
+    const int n_slices = (width + kTK - 1) / kTK;
+    for (int it = 0; it < n_slices; ++it) {
+        const int buf = it & 1;
+        if (it + 1 < n_slices) stage_slice(buf ^ 1, (it + 1) * kTK);
+        moe_cp_commit();
+        moe_cp_wait_all_but_one();
+        __syncthreads();
+        const __nv_bfloat16* xs = stage + buf * 3 * kTile;
+        moe_warp_product(g, xs + a_off, xs + kTile + b_off);
+        moe_warp_product(u, xs + a_off, xs + 2 * kTile + b_off);
+        __syncthreads();
+    }
+    const int r0 = warp * 16 + quad, r1 = r0 + 8;
+    const int p0 = first + r0, p1 = first + r1;
+    const float s0 = scale_of[r0], s1 = scale_of[r1];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int c = c0 + 8 * j + pair;
+        if (c < ff) {                                   // ff is even: c + 1 < ff as well
+            if (p0 < last) {
+                const float x = s0 * g[j][0], y = s0 * g[j][1];
+                *reinterpret_cast<__nv_bfloat162*>(act + (size_t)p0 * ff + c) =
+                    __floats2bfloat162_rn(x / (1.0f + expf(-x)) * (s0 * u[j][0]), y / (1.0f + expf(-y)) * (s0 * u[j][1]));
+            }
+            if (p1 < last) {
+                const float x = s1 * g[j][2], y = s1 * g[j][3];
+                *reinterpret_cast<__nv_bfloat162*>(act + (size_t)p1 * ff + c) =
+                    __floats2bfloat162_rn(x / (1.0f + expf(-x)) * (s1 * u[j][2]), y / (1.0f + expf(-y)) * (s1 * u[j][3]));
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(128) moe_down_tc_kernel(const __nv_bfloat16* __restrict__ act, const int* __restrict__ offsets,
+                                                          const __nv_bfloat16* __restrict__ w_down, float* __restrict__ y, int width, int ff,
+                                                          int n_experts) {
+    extern __shared__ __align__(16) unsigned char moe_smem[];
+    __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(moe_smem);      // 2 x (x, weight)
+    int e, first, last;
+    if (!moe_find_tile(offsets, n_experts, blockIdx.x, &e, &first, &last, kTM)) return;
+    const int c0 = blockIdx.y * kTN;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, quad = lane >> 2, pair = (lane & 3) * 2;
+    const int lrow = lane & 7, lmat = lane >> 3;
+    const __nv_bfloat16* wd = w_down + (size_t)e * width * ff;
+    auto stage_slice = [&](int buf, int k0) {
+        __nv_bfloat16* xs = stage + buf * 2 * kTile;
+        for (int idx = threadIdx.x; idx < kTM * (kTK / 8); idx += blockDim.x) {
+            const int r = idx / (kTK / 8), kk = (idx % (kTK / 8)) * 8;
+            const bool in = first + r < last && k0 + kk < ff;
+            moe_cp16(xs + r * kTStride + kk, in ? act + (size_t)(first + r) * ff + k0 + kk : act, in);
+        }
+        moe_stage_weight(xs + kTile, wd, width, ff, c0, k0);
+    };
+    float acc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    const int a_off = (warp * 16 + lrow + (lmat & 1) * 8) * kTStride + (lmat >> 1) * 8;
+    const int b_off = (lrow + (lmat >> 1) * 8) * kTStride + (lmat & 1) * 8;
+    stage_slice(0, 0);
+    moe_cp_commit();
+    const int n_slices = (ff + kTK - 1) / kTK;
+    for (int it = 0; it < n_slices; ++it) {
+        const int buf = it & 1;
+        if (it + 1 < n_slices) stage_slice(buf ^ 1, (it + 1) * kTK);
+        moe_cp_commit();
+        moe_cp_wait_all_but_one();
+        __syncthreads();
+        const __nv_bfloat16* xs = stage + buf * 2 * kTile;
+        moe_warp_product(acc, xs + a_off, xs + kTile + b_off);
+        __syncthreads();
+    }
+    const int p0 = first + warp * 16 + quad, p1 = p0 + 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int c = c0 + 8 * j + pair;
+        if (c < width) {                                // width is even
+            if (p0 < last) *reinterpret_cast<float2*>(y + (size_t)p0 * width + c) = make_float2(acc[j][0], acc[j][1]);
+            if (p1 < last) *reinterpret_cast<float2*>(y + (size_t)p1 * width + c) = make_float2(acc[j][2], acc[j][3]);
+        }
+    }
+}
+
 BLM_API int blm_moe_experts(const void* h, int dtype, const float* weights, const int* order, const int* offsets, const void* w_gu,
                             const void* w_down, void* act, float* y, int n_tokens, int width, int ff, int n_experts, int top,
                             int scale_input, cudaStream_t stream) {
@@ -264,6 +444,16 @@ BLM_API int blm_moe_experts(const void* h, int dtype, const float* weights, cons
         moe_gate_up_kernel<float><<<g1, 256, 0, stream>>>((const float*)h, weights, order, offsets, (const float*)w_gu, (float*)act, width,
                                                           ff, n_experts, top, scale_input);
         moe_down_kernel<float><<<g2, 256, 0, stream>>>((const float*)act, offsets, (const float*)w_down, y, width, ff, n_experts);
+    } else if (dtype == BLM_BF16 && width % 8 == 0 && ff % 8 == 0) {
+        const long long t64 = (pairs + kTM - 1) / kTM + n_experts;
+        const dim3 t1((unsigned)t64, (unsigned)((ff + kTN - 1) / kTN)), t2((unsigned)t64, (unsigned)((width + kTN - 1) / kTN));
+        const int smem1 = 2 * 3 * kTile * (int)sizeof(__nv_bfloat16), smem2 = 2 * 2 * kTile * (int)sizeof(__nv_bfloat16);
+        cudaError_t err = cudaFuncSetAttribute(moe_gate_up_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1);
+        if (err != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "moe_experts: %s", cudaGetErrorString(err));
+        moe_gate_up_tc_kernel<<<t1, 128, smem1, stream>>>((const __nv_bfloat16*)h, weights, order, offsets, (const __nv_bfloat16*)w_gu,
+                                                          (__nv_bfloat16*)act, width, ff, n_experts, top, scale_input);
+        moe_down_tc_kernel<<<t2, 128, smem2, stream>>>((const __nv_bfloat16*)act, offsets, (const __nv_bfloat16*)w_down, y, width, ff,
+                                                       n_experts);
     } else if (dtype == BLM_BF16) {
         moe_gate_up_kernel<__nv_bfloat16><<<g1, 256, 0, stream>>>((const __nv_bfloat16*)h, weights, order, offsets,
                                                                   (const __nv_bfloat16*)w_gu, (__nv_bfloat16*)act, width, ff, n_experts,

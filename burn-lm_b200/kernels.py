@@ -92,8 +92,10 @@ _protos = {
                                c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p, c_void_p, c_void_p,
                                c_void_p, c_int, c_void_p],
         "blm_attention_sink": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                               c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                               c_void_p],
+                               c_void_p, c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                               c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "blm_attention_sink_prompt_takes": [c_int, c_int, c_int, c_int, c_int, c_int],
+        "blm_attention_sink_decode_takes": [c_int, c_int, c_int, c_int, c_int, c_int],
     },
     "moe": {
         "blm_moe_route": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
@@ -326,24 +328,54 @@ def qk_norm_append(proj, step, pool, block_table, q_out, n_heads, n_kv, key_dim,
           _ptr(block_table), block_table.shape[1], _stream())
 
 
+def attention_sink_scratch_floats(n_tokens, n_heads, value_dim, n_splits) -> int:
+    return 0 if n_splits <= 1 else n_tokens * n_heads * n_splits * (value_dim + 2)
+
+
+def attention_sink_prompt_takes(dtype, key_dim, value_dim, max_q_len, n_heads) -> bool:
+    """Whether a step of this shape runs the tensor-core prompt kernel (else the row kernel, which takes every shape)."""
+    return bool(_lib("attention_sink").blm_attention_sink_prompt_takes(_code(dtype), key_dim, value_dim, PAGE, max_q_len, n_heads))
+
+
+def attention_sink_decode_takes(dtype, key_dim, value_dim, n_heads, n_kv) -> bool:
+    """Whether single tokens and short portions of this shape run the tensor-core decode kernel, whose splits are cut by
+    pages (else the row kernel, which takes every shape and cuts its splits by chunks of 32 keys)."""
+    return bool(_lib("attention_sink").blm_attention_sink_decode_takes(_code(dtype), key_dim, value_dim, PAGE, n_heads, n_kv))
+
+
 def attention_sink(q, step, pool, block_table, out, n_heads, n_kv, key_dim, value_dim, scale, window, keep_first=0, sink=True,
-                   gate=None, gate_stride=0):
+                   gate=None, gate_stride=0, max_q_len=1, n_splits=1, scratch=None):
     """Attention of the step's tokens over the paged cache (after the append) where the query at position i sees the
     key at j when j <= i and (i - j < window or j < keep_first); softmax with `sink` added to its denominator (one more
     entry of score 0 without a value); keys of `key_dim` and values of `value_dim` lanes; `gate`: a float32 tensor
     whose element n * gate_stride + h is squashed by a sigmoid and multiplies head h's output of token n.
-    q [N, n_heads key_dim] and out [N, n_heads value_dim] in the cache's dtype."""
-    _need_cuda(q, pool, block_table, out)
+    q [N, n_heads key_dim] and out [N, n_heads value_dim] in the cache's dtype.
+
+    `max_q_len`: the longest run of new tokens of one sequence (a bound is enough): bfloat16 steps of 8 or more run
+    the tensor-core prompt kernel, 64 query rows a block (it reads step.cu_seqlens and step.start_pos); shorter ones
+    the tensor-core decode kernel (bfloat16, up to 16 query heads a kv head) or else the row kernel, a block per (row,
+    kv head) either, whose keys `n_splits` > 1 cuts over that many blocks (it then needs `scratch`:
+    attention_sink_scratch_floats(...) float32)."""
+    _need_cuda(q, pool, block_table, out, scratch)
     n = q.shape[0]
     if tuple(q.shape) != (n, n_heads * key_dim) or tuple(out.shape) != (n, n_heads * value_dim) or q.dtype != pool.dtype \
             or out.dtype != pool.dtype:
         raise KernelError("attention_sink: q [N, heads * key_dim] and out [N, heads * value_dim] in the cache's dtype")
     if gate is not None and (not gate.is_cuda or gate.dtype != torch.float32):
         raise KernelError("attention_sink: the gate is float32")
+    prompt = attention_sink_prompt_takes(pool.dtype, key_dim, value_dim, max_q_len, n_heads) and getattr(step, "cu_seqlens", None) is not None
+    if prompt:
+        n_splits = 1
+    if n_splits > 1:
+        need = attention_sink_scratch_floats(n, n_heads, value_dim, n_splits)
+        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
+            raise KernelError(f"attention_sink: {n_splits} splits need {need} float32 of scratch")
+    cu = step.cu_seqlens if prompt else None
     _call("attention_sink", "blm_attention_sink", _ptr(q), _ptr(pool), _code(pool.dtype), _flat_pool(pool, n_kv, key_dim, value_dim),
-          _ptr(block_table), block_table.shape[1], _ptr(step.token_seq), _ptr(step.token_pos), _ptr(step.slot_of_seq), _ptr(gate),
-          int(gate_stride), _ptr(out), n, n_heads, n_kv, key_dim, value_dim, PAGE, int(window), int(keep_first), c_float(scale),
-          1 if sink else 0, _stream())
+          _ptr(block_table), block_table.shape[1], _ptr(step.token_seq), _ptr(step.token_pos), _ptr(step.slot_of_seq), _ptr(cu),
+          _ptr(step.start_pos if prompt else None), (cu.numel() - 1) if prompt else 0, int(max_q_len), _ptr(gate), int(gate_stride),
+          _ptr(out), _ptr(scratch), int(n_splits), n, n_heads, n_kv, key_dim, value_dim, PAGE, int(window), int(keep_first),
+          c_float(scale), 1 if sink else 0, _stream(), kernels=2 if n_splits > 1 else 1)
 
 
 def moe_route(h, router, top):

@@ -24,6 +24,8 @@ from ..weights.loader import TensorSpec
 from .base import CacheNeed, Part
 from .linear import Linear
 
+BLOCKS_PER_SM = 4     # blocks of the row kernel a step should offer every multiprocessor
+
 
 @dataclass(frozen=True)
 class SinkAttentionSpec:
@@ -91,6 +93,20 @@ class SinkAttention(Part):
         return CacheNeed("kv", n_kv_heads=s.n_kv_heads, head_dim=s.head_dim, window=s.window, value_dim=s.value_dim,
                          keep_first=s.keep_first)
 
+    def _splits(self, step) -> int:
+        """Over how many blocks the row kernel cuts a row's keys: a few tokens with long windows leave most of the
+        multiprocessors idle otherwise.  Every block should still have some chunks of 32 keys."""
+        s = self.spec
+        if K.attention_sink_prompt_takes(self.runtime.dtype, s.head_dim, s.value_dim, step.max_q_len, s.n_heads):
+            return 1
+        seen = min(step.max_kv_len, s.window + s.keep_first)
+        blocks = step.n_tokens * s.n_kv_heads
+        want = BLOCKS_PER_SM * K.sm_count(self.runtime.device)
+        if K.attention_sink_decode_takes(self.runtime.dtype, s.head_dim, s.value_dim, s.n_heads, s.n_kv_heads):
+            pages = seen // K.PAGE + 1                       # that kernel cuts by pages: two or more to a block
+            return max(1, min((want + blocks - 1) // blocks, pages // 2, 32))
+        return max(1, min((want + blocks - 1) // blocks, seen // 128, 32))
+
     adds_to_stream = True
 
     def forward(self, x, step, cache, stream=None):
@@ -114,7 +130,11 @@ class SinkAttention(Part):
                          values_in=values_in, values_out=values_out)
         out = torch.empty((n, s.n_heads * s.value_dim), dtype=rt.dtype, device=proj.device)
         gate_at = (s.n_heads + s.n_kv_heads) * s.head_dim + v_cols
+        n_splits = self._splits(step)
+        scratch = None
+        if n_splits > 1:
+            scratch = step.workspace.scratch("attention_sink", K.attention_sink_scratch_floats(n, s.n_heads, s.value_dim, n_splits))
         K.attention_sink(q, step, cache.pool, cache.block_table, out, s.n_heads, s.n_kv_heads, s.head_dim, s.value_dim, s.scale,
                          s.window, s.keep_first, sink=s.sink, gate=proj[:, gate_at:] if s.head_gate else None,
-                         gate_stride=proj.stride(0))
+                         gate_stride=proj.stride(0), max_q_len=step.max_q_len, n_splits=n_splits, scratch=scratch)
         return self.o.into_stream(out, stream, rt.dtype, handoff=None)

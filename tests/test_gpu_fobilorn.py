@@ -30,11 +30,12 @@ def step_of(positions, seq_of=None, slots=(0,)):
     """What the kernels read of a step: the rows' sequences and positions."""
     n = len(positions)
     seq_of = list(seq_of) if seq_of is not None else [0] * n
-    cu = [0]
+    cu, starts = [0], []
     for s in range(len(slots)):
         cu.append(cu[-1] + sum(1 for x in seq_of if x == s))
+        starts.append(next((p for p, x in zip(positions, seq_of) if x == s), 0))
     return SimpleNamespace(token_seq=ints(seq_of), token_pos=ints(positions), slot_of_seq=ints(slots), cu_seqlens=ints(cu),
-                           n_tokens=n)
+                           start_pos=ints(starts), n_tokens=n)
 
 
 def engine_for(folder, dtype, max_tokens=4096, **kw):
@@ -115,9 +116,11 @@ def test_pair_embedding_keeps_the_previous_token_by_position():
     assert np.abs(out.cpu().numpy() - (table[[3, 4]] + pairs[buckets])).max() < 1e-5
 
 
-def _append_and_attend(dtype, q, k, v, positions, block_table, n_pages, scale, window, keep, sink=True, gate=None, pool=None):
+def _append_and_attend(dtype, q, k, v, positions, block_table, n_pages, scale, window, keep, sink=True, gate=None, pool=None,
+                       n_splits=1):
     """Append rows (one sequence in slot 0) and attend; q [T, H, dk], k [T, G, dk], v [T, G, dv] given as they enter the
-    scores (no norm).  Returns (out [T, H, dv], pool)."""
+    scores (no norm).  Returns (out [T, H, dv], pool).  Portions of 8 rows and more in bfloat16 with sizes in multiples of
+    8 run the tensor-core prompt kernel, all else the row kernel (its keys cut over `n_splits` blocks)."""
     from burn_lm_b200 import kernels as K
     T, H, dk = q.shape
     G, dv = k.shape[1], v.shape[2]
@@ -129,8 +132,10 @@ def _append_and_attend(dtype, q, k, v, positions, block_table, n_pages, scale, w
     q_out = torch.empty((T, H * dk), dtype=dtype, device="cuda")
     K.qk_norm_append(proj, st, pool, block_table, q_out, H, G, dk, dv)
     out = torch.empty((T, H * dv), dtype=dtype, device="cuda")
+    scratch = torch.empty(K.attention_sink_scratch_floats(T, H, dv, n_splits), dtype=torch.float32, device="cuda") if n_splits > 1 else None
     K.attention_sink(q_out, st, pool, block_table, out, H, G, dk, dv, scale, window, keep, sink=sink,
-                     gate=proj[:, (H + G) * dk + G * dv:] if gate is not None else None, gate_stride=proj.stride(0))
+                     gate=proj[:, (H + G) * dk + G * dv:] if gate is not None else None, gate_stride=proj.stride(0),
+                     max_q_len=T, n_splits=n_splits, scratch=scratch)
     return out.float().cpu().numpy().reshape(T, H, dv), pool
 
 
@@ -150,12 +155,12 @@ def test_attention_against_plain_in_prompts_and_token_by_token(dtype, H, G, dk, 
                      for h in range(H)], axis=1)
     block_table = ints([5, 2, 7, 0, 3, 0, 0, 0]).reshape(1, 8)
     tol = 2e-5 if dtype == torch.float32 else 2e-2
-    for cuts in ([T], [64, 1, 63, 2, 70], [130] + [1] * 70):
+    for cuts in ([T], [64, 1, 63, 2, 70], [130] + [1] * 70, [9, 100, 7, 84]):
         pool, at = None, 0
         for n in cuts:
             sl = slice(at, at + n)
             got, pool = _append_and_attend(dtype, q[sl], k[sl], v[sl], range(at, at + n), block_table, 8, scale, window, keep,
-                                           gate=gate[sl], pool=pool)
+                                           gate=gate[sl], pool=pool, n_splits=3 if n < 8 and at > 100 else 1)
             assert np.abs(got - want[sl]).max() < tol * np.abs(want).max(), (cuts[:3], at, n)
             at += n
     # without the sink and without a gate the same kernel is a plain windowed softmax
@@ -165,7 +170,8 @@ def test_attention_against_plain_in_prompts_and_token_by_token(dtype, H, G, dk, 
     assert np.abs(plain - want).max() > 0.05          # and the sink is not nothing
 
 
-def test_one_key_that_stands_out_is_seen_exactly_where_the_mask_says():
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_one_key_that_stands_out_is_seen_exactly_where_the_mask_says(dtype):
     """One key's score is made to tower over all others and its value is a mark of its own.  Far back among hundreds,
     at the borders of pages, just inside and just outside the window and the kept first tokens: the output is the
     mark exactly when the design lets the query see the key, in a prompt's step and for a token decoded alone."""
@@ -181,17 +187,23 @@ def test_one_key_that_stands_out_is_seen_exactly_where_the_mask_says():
         u[j % dk] = 1.0
         k[j, 0], q[i, 0] = 40.0 * u, u
         v[j, 0] = 5.0 + np.arange(dv)
+        if dtype == torch.bfloat16:
+            q, k, v = (dev(t, dtype).float().cpu().numpy().astype(np.float64) for t in (q, k, v))
+        tol = 1e-4 if dtype == torch.float32 else 1e-1     # marks of 5 to 12 in bfloat16
         sees = P.visible(i, j, window, keep)
         assert sees == (j <= i and (i - j < window or j < keep))
         want = P.attend(q[:, 0], k[:, 0], v[:, 0], scale, window, keep)
         assert (np.abs(want[i] - v[j, 0]).max() < 1e-3) == sees, (i, j)
         # the prompt in one step
-        got, pool = _append_and_attend(torch.float32, q, k, v, range(T), block_table, 8, scale, window, keep)
-        assert np.abs(got[:, 0] - want).max() < 1e-4, ("prompt", i, j)
-        # the query decoded alone over the cache the prompt left
-        one, _ = _append_and_attend(torch.float32, q[i:i + 1], k[i:i + 1], v[i:i + 1], [i], block_table, 8, scale, window, keep, pool=pool)
-        assert np.abs(one[0, 0] - want[i]).max() < 1e-4, ("decoded", i, j)
-        assert (np.abs(one[0, 0] - v[j, 0]).max() < 1e-3) == sees, ("decoded", i, j)
+        got, pool = _append_and_attend(dtype, q, k, v, range(T), block_table, 8, scale, window, keep)
+        assert np.abs(got[:, 0] - want).max() < tol, ("prompt", i, j)
+        assert (np.abs(got[i, 0] - v[j, 0]).max() < 10 * tol) == sees, ("prompt", i, j)
+        # the query decoded alone over the cache the prompt left, its keys in one block and cut over several
+        for n_splits in (1, 4):
+            one, _ = _append_and_attend(dtype, q[i:i + 1], k[i:i + 1], v[i:i + 1], [i], block_table, 8, scale, window, keep, pool=pool,
+                                        n_splits=n_splits)
+            assert np.abs(one[0, 0] - want[i]).max() < tol, ("decoded", i, j, n_splits)
+            assert (np.abs(one[0, 0] - v[j, 0]).max() < 10 * tol) == sees, ("decoded", i, j, n_splits)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -261,6 +273,38 @@ def test_mixture_of_experts_against_plain(dtype, experts, top, ff, shared):
     assert np.abs(got - want_in).max() < tol * np.abs(want_in).max()
     got = K.moe_experts(h, ids, weights, gate_up, down, extra=extra, weight_on_input=False).float().cpu().numpy()
     assert np.abs(got - want_out).max() < tol * np.abs(want_out).max()
+
+
+def test_rows_of_no_sequence_may_hold_anything():
+    """A captured prompt step is padded with rows that belong to no sequence; after the first layer they may hold
+    anything, a NaN too.  The router still names experts that exist for them, the other rows' results do not change,
+    and the prompt kernel leaves zeros in them."""
+    from burn_lm_b200 import kernels as K
+    rng = np.random.default_rng(6)
+    n, d, experts, top, ff = 40, 32, 5, 2, 16
+    h = dev(rng.normal(size=(n, d)), torch.bfloat16)
+    router = dev(rng.normal(size=(experts, d)))
+    gate_up = dev(rng.normal(size=(experts, 2 * ff, d)) * 0.3, torch.bfloat16)
+    down = dev(rng.normal(size=(experts, d, ff)) * 0.3, torch.bfloat16)
+    ids, w = K.moe_route(h, router, top)
+    clean = K.moe_experts(h, ids, w, gate_up, down)
+    h2 = h.clone()
+    h2[33:] = float("nan")
+    ids2, w2 = K.moe_route(h2, router, top)
+    assert int(ids2.min()) >= 0 and int(ids2.max()) < experts
+    got = K.moe_experts(h2, ids2, w2, gate_up, down)
+    assert torch.equal(got[:33], clean[:33])
+    # the prompt kernel: 20 rows of a sequence, 12 of none
+    H, G, dk, dv = 2, 1, 16, 8
+    pool = torch.zeros((2, K.kv_page_elems(G, dk, dv)), dtype=torch.bfloat16, device="cuda")
+    st = step_of(list(range(20)) + [0] * 12, [0] * 20 + [-1] * 12)
+    proj = dev(rng.normal(size=(32, (H + G) * dk + G * dv)))
+    q = torch.empty((32, H * dk), dtype=torch.bfloat16, device="cuda")
+    bt = ints([1, 0]).reshape(1, 2)
+    K.qk_norm_append(proj, st, pool, bt, q, H, G, dk, dv)
+    out = torch.full((32, H * dv), float("nan"), dtype=torch.bfloat16, device="cuda")
+    K.attention_sink(q, st, pool, bt, out, H, G, dk, dv, 0.5, 16, 2, max_q_len=32)
+    assert bool(torch.isfinite(out).all()) and float(out[20:].abs().max()) == 0.0 and float(out[:20].abs().max()) > 0.0
 
 
 # ---------------------------------------------------------------------------------------------------------
