@@ -349,6 +349,22 @@ __device__ __forceinline__ void cp_async16(__nv_bfloat16* dst, const __nv_bfloat
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all_but_one() { asm volatile("cp.async.wait_group 1;\n" ::: "memory"); }
 
+// 2^x by the special function unit (the scores are in units of log 2; -inf gives 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// zeros where no copy will write: rows [row_begin, n_rows) of a staged operand wholly, and lanes [used, stride) of the others
+__device__ __forceinline__ void zero_unwritten(__nv_bfloat16* buf, int n_rows, int stride, int row_begin, int used) {
+    const int vec = stride / 8;
+    for (int idx = threadIdx.x; idx < n_rows * vec; idx += blockDim.x) {
+        const int r = idx / vec, c = (idx % vec) * 8;
+        if (r >= row_begin || c >= used) *reinterpret_cast<uint4*>(buf + r * stride + c) = make_uint4(0u, 0u, 0u, 0u);
+    }
+}
+
 constexpr int kTileQ = 64, kTileK = 64;
 
 // The pages a query tile walks: `kept` pages from the sequence's start, then pages wp0 .. wp1.
@@ -363,19 +379,41 @@ struct PageWalk {
     __device__ __forceinline__ int page(int it) const { return it < kept ? it : wp0 + (it - kept); }
 };
 
+// How one thread of a block walks a [rows][vec] grid of 16-byte groups that the block's threads share out in turn:
+// where it starts and how far a step of blockDim groups takes it (worked out once: the walk itself divides nothing).
+struct GroupWalk {
+    int r, c, dr, dc, vec;
+    __device__ __forceinline__ GroupWalk(int vec_) : vec(vec_) {
+        r = threadIdx.x / vec_;
+        c = threadIdx.x % vec_;
+        dr = blockDim.x / vec_;
+        dc = blockDim.x % vec_;
+    }
+};
+
 // one page's keys and values of one kv head into a buffer pair (every thread of the block takes its share)
 __device__ __forceinline__ void stage_page(__nv_bfloat16* kbuf, __nv_bfloat16* vbuf, const __nv_bfloat16* page, int n_kv, int kvh, int dk,
-                                           int dv, int qstride, int vstride, int first_pos, int p_last) {
+                                           int dv, int qstride, int vstride, int first_pos, int p_last, const GroupWalk& kw,
+                                           const GroupWalk& vw) {
     const __nv_bfloat16* kpage = page + (size_t)kvh * kTileK * dk;
     const __nv_bfloat16* vpage = page + (size_t)n_kv * kTileK * dk + (size_t)kvh * kTileK * dv;
-    const int kvec = dk / 8, vvec = dv / 8;
-    for (int idx = threadIdx.x; idx < kTileK * kvec; idx += blockDim.x) {
-        const int r = idx / kvec, c = (idx % kvec) * 8;
-        cp_async16(kbuf + r * qstride + c, kpage + (size_t)r * dk + c, true);
+    for (int r = kw.r, c = kw.c; r < kTileK;) {
+        cp_async16(kbuf + r * qstride + c * 8, kpage + r * dk + c * 8, true);
+        r += kw.dr;
+        c += kw.dc;
+        if (c >= kw.vec) {
+            c -= kw.vec;
+            ++r;
+        }
     }
-    for (int idx = threadIdx.x; idx < kTileK * vvec; idx += blockDim.x) {
-        const int r = idx / vvec, c = (idx % vvec) * 8;
-        cp_async16(vbuf + r * vstride + c, vpage + (size_t)r * dv + c, first_pos + r <= p_last);
+    for (int r = vw.r, c = vw.c; r < kTileK;) {
+        cp_async16(vbuf + r * vstride + c * 8, vpage + r * dv + c * 8, first_pos + r <= p_last);
+        r += vw.dr;
+        c += vw.dc;
+        if (c >= vw.vec) {
+            c -= vw.vec;
+            ++r;
+        }
     }
 }
 
@@ -425,21 +463,23 @@ __global__ void __launch_bounds__(128) attention_sink_prompt_kernel(
     const int p0 = start_pos[seq] + t0;                // its position
     const int p_last = p0 + rows - 1;
     const int* pages = block_table + (size_t)slot_of_seq[seq] * table_stride;
-    {   // zeros everywhere first: rows of no query, lanes beyond dk and dv
-        const int total = (3 * kTileQ * qstride + 2 * kTileK * vstride) / 8;
-        for (int idx = tid; idx < total; idx += 128) reinterpret_cast<uint4*>(smem_raw)[idx] = make_uint4(0u, 0u, 0u, 0u);
-    }
-    __syncthreads();
+    // zeros where no copy writes: rows of no query, lanes beyond dk and dv (the copies take whole groups of 8 lanes)
+    zero_unwritten(Qs, kTileQ, qstride, rows, dk);
+    zero_unwritten(Kb, 2 * kTileK, qstride, 2 * kTileK, dk);
+    zero_unwritten(Vb, 2 * kTileK, vstride, 2 * kTileK, dv);
     const PageWalk walk(p0, p_last, window, keep_first);
     for (int idx = tid; idx < rows * (dk / 8); idx += 128) {
         const int r = idx / (dk / 8), c = (idx % (dk / 8)) * 8;
         cp_async16(Qs + r * qstride + c, q + ((size_t)(row0 + r) * n_heads + head) * dk + c, true);
     }
-    stage_page(Kb, Vb, pool + (size_t)pages[walk.page(0)] * page_elems, n_kv, kvh, dk, dv, qstride, vstride, walk.page(0) * kTileK, p_last);
+    const GroupWalk kw(dk / 8), vw(dv / 8);
+    stage_page(Kb, Vb, pool + (size_t)pages[walk.page(0)] * page_elems, n_kv, kvh, dk, dv, qstride, vstride, walk.page(0) * kTileK, p_last,
+               kw, vw);
     cp_async_commit();
     const int quad = lane >> 2, pair = (lane & 3) * 2;
     const int lrow = lane & 7, lmat = lane >> 3;
     const int pr0 = p0 + warp * 16 + quad, pr1 = pr0 + 8;        // positions of this thread's two rows
+    const float scale2 = scale * 1.4426950408889634f;            // scores in units of log 2: the exponentials are exp2
     float m[2], l[2], o[NV][4];
     m[0] = m[1] = sink ? 0.f : -INFINITY;
     l[0] = l[1] = sink ? 0.25f : 0.f;                  // a quad's four lanes add up to the sink's one
@@ -451,7 +491,7 @@ __global__ void __launch_bounds__(128) attention_sink_prompt_kernel(
         if (it + 1 < walk.n_tiles) {
             const int pg = walk.page(it + 1);
             stage_page(Kb + (buf ^ 1) * kTileK * qstride, Vb + (buf ^ 1) * kTileK * vstride, pool + (size_t)pages[pg] * page_elems, n_kv, kvh,
-                       dk, dv, qstride, vstride, pg * kTileK, p_last);
+                       dk, dv, qstride, vstride, pg * kTileK, p_last, kw, vw);
         }
         cp_async_commit();
         cp_async_wait_all_but_one();                   // this tile (and the queries) have landed; the next may be on its way
@@ -473,40 +513,54 @@ __global__ void __launch_bounds__(128) attention_sink_prompt_kernel(
             }
         }
         float mx0 = -INFINITY, mx1 = -INFINITY;
+        // every row of this warp sees every key of the page when the page lies behind the warp's first row and inside
+        // the window of its last (or among the kept first tokens): then nothing is masked (most pages of a long window)
+        const int w_first = p0 + warp * 16, w_last = w_first + 15, key0 = pg * kTileK;
+        if (key0 + kTileK - 1 <= w_first && (w_last - key0 < window || key0 + kTileK <= keep_first)) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int key = pg * kTileK + 8 * j + pair + (e & 1);
-                const int pr = e < 2 ? pr0 : pr1;
-                const bool sees = key <= pr && (pr - key < window || key < keep_first);
-                const float v = sees ? s[j][e] * scale : -INFINITY;
-                s[j][e] = v;
-                if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+            for (int j = 0; j < 8; ++j) {
+                mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
+                mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
             }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = key0 + 8 * j + pair + (e & 1);
+                    const int pr = e < 2 ? pr0 : pr1;
+                    const bool sees = key <= pr && (pr - key < window || key < keep_first);
+                    const float v = sees ? s[j][e] : -INFINITY;
+                    s[j][e] = v;
+                    if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+                }
+        }
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
+        // the running maxima are kept in units of log 2 (scale2 > 0: the largest raw score is the largest score)
+        const float mn0 = fmaxf(m[0], mx0 * scale2), mn1 = fmaxf(m[1], mx1 * scale2);
         const float use0 = mn0 == -INFINITY ? 0.f : mn0, use1 = mn1 == -INFINITY ? 0.f : mn1;    // a row that has seen no key yet
-        const float corr0 = expf(m[0] - use0), corr1 = expf(m[1] - use1);
+        const float corr0 = fast_exp2(m[0] - use0), corr1 = fast_exp2(m[1] - use1);
         m[0] = mn0;
         m[1] = mn1;
         float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            s[j][0] = expf(s[j][0] - use0); s[j][1] = expf(s[j][1] - use0);
-            s[j][2] = expf(s[j][2] - use1); s[j][3] = expf(s[j][3] - use1);
+            s[j][0] = fast_exp2(fmaf(s[j][0], scale2, -use0)); s[j][1] = fast_exp2(fmaf(s[j][1], scale2, -use0));
+            s[j][2] = fast_exp2(fmaf(s[j][2], scale2, -use1)); s[j][3] = fast_exp2(fmaf(s[j][3], scale2, -use1));
             sum0 += s[j][0] + s[j][1];
             sum1 += s[j][2] + s[j][3];
         }
         l[0] = l[0] * corr0 + sum0;
         l[1] = l[1] * corr1 + sum1;
+        if (corr0 != 1.f || corr1 != 1.f) {            // once the maxima have settled there is nothing to rescale
 #pragma unroll
-        for (int j = 0; j < NV; ++j) {
-            o[j][0] *= corr0; o[j][1] *= corr0;
-            o[j][2] *= corr1; o[j][3] *= corr1;
+            for (int j = 0; j < NV; ++j) {
+                o[j][0] *= corr0; o[j][1] *= corr0;
+                o[j][2] *= corr1; o[j][3] *= corr1;
+            }
         }
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {               // 16 keys a step: two of the score tiles make one operand
@@ -559,6 +613,7 @@ static int launch_prompt(const void* q, const void* pool, long long page_elems, 
         cudaError_t e = cudaFuncSetAttribute(attention_sink_prompt_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "attention_sink: %s", cudaGetErrorString(e));
     }
+    cudaFuncSetAttribute(attention_sink_prompt_kernel<NV>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     const unsigned tiles = (unsigned)((n_tokens + kTileQ - 1) / kTileQ + n_seqs);     // every sequence may end in a tile that is not full
     attention_sink_prompt_kernel<NV><<<dim3(tiles, n_heads), 128, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)pool, page_elems, block_table, table_stride, cu_seqlens, start_pos, slot_of_seq,
@@ -566,7 +621,12 @@ static int launch_prompt(const void* q, const void* pool, long long page_elems, 
     return blm_check_launch("attention_sink (prompt)");
 }
 
-template <int NV>
+// kDecodeStages pages in shared memory, one worked on and the others on their way.  Measured with 64 sequences of
+// 1,088 tokens on 8 kv heads: heads of 64 lanes 45 us with two stages (five blocks to a multiprocessor), 60 with three,
+// 61 with four; heads of 128 lanes 84, 79 and 121 us.
+template <int N> __device__ __forceinline__ void cp_async_wait_all_but() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+template <int NV, int kDecodeStages>
 __global__ void __launch_bounds__(128) attention_sink_decode_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pool, long long page_elems,
     const int* __restrict__ block_table, int table_stride, const int* __restrict__ token_seq, const int* __restrict__ token_pos,
@@ -580,8 +640,8 @@ __global__ void __launch_bounds__(128) attention_sink_decode_kernel(
     const int qstride = dkp + 8;
     constexpr int vstride = 8 * NV + 8;
     __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [16][qstride]
-    __nv_bfloat16* Kb = Qs + 16 * qstride;                               // 2 x [64][qstride]
-    __nv_bfloat16* Vb = Kb + 2 * kTileK * qstride;                       // 2 x [64][vstride]
+    __nv_bfloat16* Kb = Qs + 16 * qstride;                               // kDecodeStages x [64][qstride]
+    __nv_bfloat16* Vb = Kb + kDecodeStages * kTileK * qstride;           // kDecodeStages x [64][vstride]
     const int seq = token_seq[n];
     const int head0 = kvh * group;
     if (seq < 0) {                                     // a row of no sequence: zeros, nothing read
@@ -596,11 +656,9 @@ __global__ void __launch_bounds__(128) attention_sink_decode_kernel(
     }
     const int pos = token_pos[n];
     const int* pages = block_table + (size_t)slot_of_seq[seq] * table_stride;
-    {
-        const int total = (16 * qstride + 2 * kTileK * qstride + 2 * kTileK * vstride) / 8;
-        for (int idx = tid; idx < total; idx += 128) reinterpret_cast<uint4*>(smem_raw)[idx] = make_uint4(0u, 0u, 0u, 0u);
-    }
-    __syncthreads();
+    zero_unwritten(Qs, 16, qstride, group, dk);
+    zero_unwritten(Kb, kDecodeStages * kTileK, qstride, kDecodeStages * kTileK, dk);
+    zero_unwritten(Vb, kDecodeStages * kTileK, vstride, kDecodeStages * kTileK, dv);
     const PageWalk walk(pos, pos, window, keep_first);
     const int per_split = (walk.n_tiles + n_splits - 1) / n_splits;
     const int it_begin = split * per_split, it_end = min(walk.n_tiles, it_begin + per_split);
@@ -608,13 +666,21 @@ __global__ void __launch_bounds__(128) attention_sink_decode_kernel(
         const int r = idx / (dk / 8), c = (idx % (dk / 8)) * 8;
         cp_async16(Qs + r * qstride + c, q + ((size_t)n * n_heads + head0 + r) * dk + c, true);
     }
-    if (it_begin < it_end)
-        stage_page(Kb, Vb, pool + (size_t)pages[walk.page(it_begin)] * page_elems, n_kv, kvh, dk, dv, qstride, vstride,
-                   walk.page(it_begin) * kTileK, pos);
-    cp_async_commit();
+    const GroupWalk kw(dk / 8), vw(dv / 8);
+    auto fetch = [&](int it) {                         // page `it` of the walk into its place in the ring
+        const int pg = walk.page(it), b = (it - it_begin) % kDecodeStages;
+        stage_page(Kb + b * kTileK * qstride, Vb + b * kTileK * vstride, pool + (size_t)pages[pg] * page_elems, n_kv, kvh, dk, dv, qstride,
+                   vstride, pg * kTileK, pos, kw, vw);
+    };
+#pragma unroll
+    for (int ahead = 0; ahead < kDecodeStages - 1; ++ahead) {
+        if (it_begin + ahead < it_end) fetch(it_begin + ahead);
+        cp_async_commit();
+    }
     const int quad = lane >> 2, pair = (lane & 3) * 2;
     const int lrow = lane & 7, lmat = lane >> 3;
     const bool with_sink = sink && split == 0 && warp == 0;      // the sink is counted once
+    const float scale2 = scale * 1.4426950408889634f;            // scores in units of log 2: the exponentials are exp2
     float m[2], l[2], o[NV][4];
     m[0] = m[1] = with_sink ? 0.f : -INFINITY;
     l[0] = l[1] = with_sink ? 0.25f : 0.f;
@@ -622,14 +688,10 @@ __global__ void __launch_bounds__(128) attention_sink_decode_kernel(
     for (int j = 0; j < NV; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
     const __nv_bfloat16* qa = Qs + (lrow + (lmat & 1) * 8) * qstride + (lmat >> 1) * 8;
     for (int it = it_begin; it < it_end; ++it) {
-        const int buf = (it - it_begin) & 1;
-        if (it + 1 < it_end) {
-            const int pg = walk.page(it + 1);
-            stage_page(Kb + (buf ^ 1) * kTileK * qstride, Vb + (buf ^ 1) * kTileK * vstride, pool + (size_t)pages[pg] * page_elems, n_kv, kvh,
-                       dk, dv, qstride, vstride, pg * kTileK, pos);
-        }
+        const int buf = (it - it_begin) % kDecodeStages;
+        if (it + kDecodeStages - 1 < it_end) fetch(it + kDecodeStages - 1);      // into the buffer the page before this one has left
         cp_async_commit();
-        cp_async_wait_all_but_one();
+        cp_async_wait_all_but<kDecodeStages - 1>();    // this page (and the queries) have landed; the others may be on their way
         __syncthreads();
         const int pg = walk.page(it);
         // this warp's 16 keys of the page
@@ -644,14 +706,14 @@ __global__ void __launch_bounds__(128) attention_sink_decode_kernel(
             mma_bf16(s[0], a, b[0], b[1]);
             mma_bf16(s[1], a, b[2], b[3]);
         }
-        float mx = -INFINITY;                          // every row (head) sees the same keys
+        // every row (head) sees the same keys
 #pragma unroll
         for (int j = 0; j < 2; ++j)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int key = pg * kTileK + 16 * warp + 8 * j + pair + (e & 1);
                 const bool sees = key <= pos && (pos - key < window || key < keep_first);
-                s[j][e] = sees ? s[j][e] * scale : -INFINITY;
+                s[j][e] = sees ? s[j][e] * scale2 : -INFINITY;
             }
         float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
         float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
@@ -659,17 +721,16 @@ __global__ void __launch_bounds__(128) attention_sink_decode_kernel(
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        (void)mx;
         const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
         const float use0 = mn0 == -INFINITY ? 0.f : mn0, use1 = mn1 == -INFINITY ? 0.f : mn1;
-        const float corr0 = expf(m[0] - use0), corr1 = expf(m[1] - use1);
+        const float corr0 = fast_exp2(m[0] - use0), corr1 = fast_exp2(m[1] - use1);
         m[0] = mn0;
         m[1] = mn1;
         float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-            s[j][0] = expf(s[j][0] - use0); s[j][1] = expf(s[j][1] - use0);
-            s[j][2] = expf(s[j][2] - use1); s[j][3] = expf(s[j][3] - use1);
+            s[j][0] = fast_exp2(s[j][0] - use0); s[j][1] = fast_exp2(s[j][1] - use0);
+            s[j][2] = fast_exp2(s[j][2] - use1); s[j][3] = fast_exp2(s[j][3] - use1);
             sum0 += s[j][0] + s[j][1];
             sum1 += s[j][2] + s[j][3];
         }
@@ -720,7 +781,7 @@ __global__ void __launch_bounds__(128) attention_sink_decode_kernel(
         for (int w = 0; w < 4; ++w) {
             const float* src = sh + ((size_t)w * 16 + r) * rstride;
             if (src[0] > -INFINITY) {
-                const float f = expf(src[0] - big);
+                const float f = fast_exp2(src[0] - big);
                 lsum += src[1] * f;
                 acc += src[2 + d] * f;
             }
@@ -729,7 +790,7 @@ __global__ void __launch_bounds__(128) attention_sink_decode_kernel(
         if (n_splits > 1) {
             float* part = partial + (((size_t)n * n_heads + head) * n_splits + split) * (dv + 2);
             if (d == 0) {
-                part[0] = big;
+                part[0] = big * 0.6931471805599453f;       // the splits are put together in natural units
                 part[1] = lsum;
             }
             part[2 + d] = acc;
@@ -740,20 +801,21 @@ __global__ void __launch_bounds__(128) attention_sink_decode_kernel(
     }
 }
 
-template <int NV>
+template <int NV, int kDecodeStages>
 static int launch_decode(const void* q, const void* pool, long long page_elems, const int* block_table, int table_stride,
                          const int* token_seq, const int* token_pos, const int* slot_of_seq, const float* gate, long long gate_stride,
                          void* out, float* partial, int n_splits, int n_tokens, int n_heads, int n_kv, int dk, int dv, int window,
                          int keep_first, float scale, int sink, cudaStream_t stream) {
     const int dkp = (dk + 15) & ~15;
-    size_t smem = ((size_t)16 * (dkp + 8) + (size_t)2 * kTileK * (dkp + 8) + (size_t)2 * kTileK * (8 * NV + 8)) * sizeof(__nv_bfloat16);
+    size_t smem = ((size_t)16 * (dkp + 8) + (size_t)kDecodeStages * kTileK * ((dkp + 8) + (8 * NV + 8))) * sizeof(__nv_bfloat16);
     const size_t merge = (size_t)16 * (dkp + 8) * sizeof(__nv_bfloat16) + (size_t)4 * 16 * (8 * NV + 2) * sizeof(float);
     if (merge > smem) smem = merge;
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(attention_sink_decode_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attention_sink_decode_kernel<NV, kDecodeStages>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "attention_sink: %s", cudaGetErrorString(e));
     }
-    attention_sink_decode_kernel<NV><<<dim3(n_tokens, n_kv, n_splits), 128, smem, stream>>>(
+    cudaFuncSetAttribute(attention_sink_decode_kernel<NV, kDecodeStages>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    attention_sink_decode_kernel<NV, kDecodeStages><<<dim3(n_tokens, n_kv, n_splits), 128, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)pool, page_elems, block_table, table_stride, token_seq, token_pos, slot_of_seq, gate,
         gate_stride, (__nv_bfloat16*)out, partial, n_heads, n_kv, dk, dv, window, keep_first, scale, sink);
     if (n_splits > 1) {
@@ -802,11 +864,11 @@ BLM_API int blm_attention_sink(const void* q, const void* pool, int dtype, long 
 #undef BLM_PROMPT
     }
     if (blm_attention_sink_decode_takes(dtype, dk, dv, page_size, n_heads, n_kv)) {
-#define BLM_DECODE(NV) launch_decode<NV>(q, pool, page_elems, block_table, table_stride, token_seq, token_pos, slot_of_seq, gate, gate_stride, \
+#define BLM_DECODE(NV, STAGES) launch_decode<NV, STAGES>(q, pool, page_elems, block_table, table_stride, token_seq, token_pos, slot_of_seq, gate, gate_stride, \
                                          out, partial, n_splits, n_tokens, n_heads, n_kv, dk, dv, window, keep_first, scale, sink, stream)
-        if (dv <= 32) return BLM_DECODE(4);
-        if (dv <= 64) return BLM_DECODE(8);
-        return BLM_DECODE(16);
+        if (dv <= 32) return BLM_DECODE(4, 2);
+        if (dv <= 64) return BLM_DECODE(8, 2);
+        return BLM_DECODE(16, 3);
 #undef BLM_DECODE
     }
     if (dtype == BLM_F32)

@@ -103,8 +103,9 @@ class SinkAttention(Part):
         blocks = step.n_tokens * s.n_kv_heads
         want = BLOCKS_PER_SM * K.sm_count(self.runtime.device)
         if K.attention_sink_decode_takes(self.runtime.dtype, s.head_dim, s.value_dim, s.n_heads, s.n_kv_heads):
-            pages = seen // K.PAGE + 1                       # that kernel cuts by pages: two or more to a block
-            return max(1, min((want + blocks - 1) // blocks, pages // 2, 32))
+            pages = seen // K.PAGE + 1                       # that kernel cuts by pages: some to every block, and its blocks
+            want //= 2                                       # hold three pages each: half as many fill a multiprocessor
+            return max(1, min((want + blocks - 1) // blocks, pages // 4, 32))
         return max(1, min((want + blocks - 1) // blocks, seen // 128, 32))
 
     adds_to_stream = True
