@@ -326,18 +326,18 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ unsigned smem_at(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
-// four 8x8 tiles of 16-bit elements: lanes 8i .. 8i + 7 give the addresses of the rows of tile i; a lane receives, of
+// four 8x8 tiles of 16-bit elements from shared memory (`a`: a 32-bit shared address, see smem_at): lanes 8i .. 8i + 7
+// give the addresses of the rows of tile i; a lane receives, of
 // every tile, the elements (lane / 4, 2 (lane % 4)) and the next (transposed: (2 (lane % 4), lane / 4) and the one below)
-__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const __nv_bfloat16* p) {
-    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], unsigned a) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
-__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const __nv_bfloat16* p) {
-    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], unsigned a) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
 // 16 bytes from global to shared memory without passing registers; `valid` false: zeros instead (nothing is read)
@@ -485,7 +485,10 @@ __global__ void __launch_bounds__(128) attention_sink_prompt_kernel(
     l[0] = l[1] = sink ? 0.25f : 0.f;                  // a quad's four lanes add up to the sink's one
 #pragma unroll
     for (int j = 0; j < NV; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
-    const __nv_bfloat16* qa = Qs + (warp * 16 + lrow + (lmat & 1) * 8) * qstride + (lmat >> 1) * 8;
+    const unsigned qa = smem_at(Qs + (warp * 16 + lrow + (lmat & 1) * 8) * qstride + (lmat >> 1) * 8);
+    const unsigned kb0 = smem_at(Kb + (lrow + (lmat >> 1) * 8) * qstride + (lmat & 1) * 8);
+    const unsigned vb0 = smem_at(Vb + (lrow + (lmat & 1) * 8) * vstride + (lmat >> 1) * 8);
+    const unsigned kstep = 16 * qstride * 2;           // bytes from 16 keys to the next 16
     for (int it = 0; it < walk.n_tiles; ++it) {
         const int buf = it & 1;
         if (it + 1 < walk.n_tiles) {
@@ -497,17 +500,16 @@ __global__ void __launch_bounds__(128) attention_sink_prompt_kernel(
         cp_async_wait_all_but_one();                   // this tile (and the queries) have landed; the next may be on its way
         __syncthreads();
         const int pg = walk.page(it);
-        const __nv_bfloat16* kb = Kb + buf * kTileK * qstride + (lrow + (lmat >> 1) * 8) * qstride + (lmat & 1) * 8;
-        const __nv_bfloat16* vb = Vb + buf * kTileK * vstride + (lrow + (lmat & 1) * 8) * vstride + (lmat >> 1) * 8;
+        const unsigned kb = kb0 + buf * kTileK * qstride * 2, vb = vb0 + buf * kTileK * vstride * 2;
         float s[8][4];
 #pragma unroll
         for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
         for (int kk = 0; kk < dkp; kk += 16) {
             uint32_t a[4], b[4];
-            ldsm_x4(a, qa + kk);
+            ldsm_x4(a, qa + kk * 2);
 #pragma unroll
             for (int jj = 0; jj < 4; ++jj) {
-                ldsm_x4(b, kb + 16 * jj * qstride + kk);
+                ldsm_x4(b, kb + jj * kstep + kk * 2);
                 mma_bf16(s[2 * jj], a, b[0], b[1]);
                 mma_bf16(s[2 * jj + 1], a, b[2], b[3]);
             }
@@ -569,7 +571,7 @@ __global__ void __launch_bounds__(128) attention_sink_prompt_kernel(
             a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]); a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
             for (int jj = 0; jj < NV / 2; ++jj) {
-                ldsm_x4_trans(b, vb + 16 * kk * vstride + 16 * jj);
+                ldsm_x4_trans(b, vb + (16 * kk * vstride + 16 * jj) * 2);
                 mma_bf16(o[2 * jj], a, b[0], b[1]);
                 mma_bf16(o[2 * jj + 1], a, b[2], b[3]);
             }
@@ -686,7 +688,10 @@ __global__ void __launch_bounds__(128) attention_sink_decode_kernel(
     l[0] = l[1] = with_sink ? 0.25f : 0.f;
 #pragma unroll
     for (int j = 0; j < NV; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
-    const __nv_bfloat16* qa = Qs + (lrow + (lmat & 1) * 8) * qstride + (lmat >> 1) * 8;
+    const unsigned qa = smem_at(Qs + (lrow + (lmat & 1) * 8) * qstride + (lmat >> 1) * 8);
+    // this warp's 16 keys of a page
+    const unsigned kb0 = smem_at(Kb + (16 * warp + lrow + (lmat >> 1) * 8) * qstride + (lmat & 1) * 8);
+    const unsigned vb0 = smem_at(Vb + (16 * warp + lrow + (lmat & 1) * 8) * vstride + (lmat >> 1) * 8);
     for (int it = it_begin; it < it_end; ++it) {
         const int buf = (it - it_begin) % kDecodeStages;
         if (it + kDecodeStages - 1 < it_end) fetch(it + kDecodeStages - 1);      // into the buffer the page before this one has left
@@ -694,15 +699,13 @@ __global__ void __launch_bounds__(128) attention_sink_decode_kernel(
         cp_async_wait_all_but<kDecodeStages - 1>();    // this page (and the queries) have landed; the others may be on their way
         __syncthreads();
         const int pg = walk.page(it);
-        // this warp's 16 keys of the page
-        const __nv_bfloat16* kb = Kb + buf * kTileK * qstride + (16 * warp + lrow + (lmat >> 1) * 8) * qstride + (lmat & 1) * 8;
-        const __nv_bfloat16* vb = Vb + buf * kTileK * vstride + (16 * warp + lrow + (lmat & 1) * 8) * vstride + (lmat >> 1) * 8;
+        const unsigned kb = kb0 + buf * kTileK * qstride * 2, vb = vb0 + buf * kTileK * vstride * 2;
         float s[2][4];
         s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
         for (int kk = 0; kk < dkp; kk += 16) {
             uint32_t a[4], b[4];
-            ldsm_x4(a, qa + kk);
-            ldsm_x4(b, kb + kk);
+            ldsm_x4(a, qa + kk * 2);
+            ldsm_x4(b, kb + kk * 2);
             mma_bf16(s[0], a, b[0], b[1]);
             mma_bf16(s[1], a, b[2], b[3]);
         }
@@ -743,7 +746,7 @@ __global__ void __launch_bounds__(128) attention_sink_decode_kernel(
         for (int jj = 0; jj < NV / 2; ++jj) {
             o[2 * jj][0] *= corr0; o[2 * jj][1] *= corr0; o[2 * jj][2] *= corr1; o[2 * jj][3] *= corr1;
             o[2 * jj + 1][0] *= corr0; o[2 * jj + 1][1] *= corr0; o[2 * jj + 1][2] *= corr1; o[2 * jj + 1][3] *= corr1;
-            ldsm_x4_trans(b, vb + 16 * jj);
+            ldsm_x4_trans(b, vb + 16 * jj * 2);
             mma_bf16(o[2 * jj], a, b[0], b[1]);
             mma_bf16(o[2 * jj + 1], a, b[2], b[3]);
         }

@@ -266,8 +266,8 @@ __device__ __forceinline__ void moe_mma(float (&c)[4], const uint32_t (&a)[4], u
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ void moe_ldsm_x4(uint32_t (&r)[4], const __nv_bfloat16* p) {
-    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+// `a`: a shared-memory address (32 bits, from __cvta_generic_to_shared once per operand: the offsets of a tile are constants)
+__device__ __forceinline__ void moe_ldsm_x4(uint32_t (&r)[4], unsigned a) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
 __device__ __forceinline__ void moe_cp16(__nv_bfloat16* dst, const __nv_bfloat16* src, bool valid) {
@@ -288,16 +288,34 @@ __device__ __forceinline__ void moe_stage_weight(__nv_bfloat16* ws, const __nv_b
 }
 
 // 16 places x 64 outputs of one warp: acc[j] += x (16 x 64 slice) . w (64 outputs x 64 slice)
-__device__ __forceinline__ void moe_warp_product(float (&acc)[8][4], const __nv_bfloat16* xa, const __nv_bfloat16* wb) {
+__device__ __forceinline__ void moe_warp_product(float (&acc)[8][4], unsigned xa, unsigned wb) {
 #pragma unroll
     for (int kk = 0; kk < kTK; kk += 16) {
         uint32_t a[4], b[4];
-        moe_ldsm_x4(a, xa + kk);
+        moe_ldsm_x4(a, xa + kk * 2);
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj) {
-            moe_ldsm_x4(b, wb + 16 * jj * kTStride + kk);
+            moe_ldsm_x4(b, wb + (16 * jj * kTStride + kk) * 2);
             moe_mma(acc[2 * jj], a, b[0], b[1]);
             moe_mma(acc[2 * jj + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+// the gate's and the up projection's sums of one slice in one pass over the tokens' operand
+__device__ __forceinline__ void moe_warp_product2(float (&g)[8][4], float (&u)[8][4], unsigned xa, unsigned gb, unsigned ub) {
+#pragma unroll
+    for (int kk = 0; kk < kTK; kk += 16) {
+        uint32_t a[4], b[4];
+        moe_ldsm_x4(a, xa + kk * 2);
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+            moe_ldsm_x4(b, gb + (16 * jj * kTStride + kk) * 2);
+            moe_mma(g[2 * jj], a, b[0], b[1]);
+            moe_mma(g[2 * jj + 1], a, b[2], b[3]);
+            moe_ldsm_x4(b, ub + (16 * jj * kTStride + kk) * 2);
+            moe_mma(u[2 * jj], a, b[0], b[1]);
+            moe_mma(u[2 * jj + 1], a, b[2], b[3]);
         }
     }
 }
@@ -346,6 +364,7 @@ __global__ void __launch_bounds__(128) moe_gate_up_tc_kernel(const __nv_bfloat16
     for (int j = 0; j < 8; ++j) g[j][0] = g[j][1] = g[j][2] = g[j][3] = u[j][0] = u[j][1] = u[j][2] = u[j][3] = 0.f;
     const int a_off = (warp * 16 + lrow + (lmat & 1) * 8) * kTStride + (lmat >> 1) * 8;
     const int b_off = (lrow + (lmat >> 1) * 8) * kTStride + (lmat & 1) * 8;
+    const unsigned stage_at = (unsigned)__cvta_generic_to_shared(stage);
     stage_slice(0, 0);
     moe_cp_commit();
     const int n_slices = (width + kTK - 1) / kTK;
@@ -355,9 +374,8 @@ __global__ void __launch_bounds__(128) moe_gate_up_tc_kernel(const __nv_bfloat16
         moe_cp_commit();
         moe_cp_wait_all_but_one();
         __syncthreads();
-        const __nv_bfloat16* xs = stage + buf * 3 * kTile;
-        moe_warp_product(g, xs + a_off, xs + kTile + b_off);
-        moe_warp_product(u, xs + a_off, xs + 2 * kTile + b_off);
+        const unsigned xs = stage_at + buf * 3 * kTile * 2;
+        moe_warp_product2(g, u, xs + a_off * 2, xs + (kTile + b_off) * 2, xs + (2 * kTile + b_off) * 2);
         __syncthreads();
     }
     const int r0 = warp * 16 + quad, r1 = r0 + 8;
@@ -406,6 +424,7 @@ __global__ void __launch_bounds__(128) moe_down_tc_kernel(const __nv_bfloat16* _
     for (int j = 0; j < 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
     const int a_off = (warp * 16 + lrow + (lmat & 1) * 8) * kTStride + (lmat >> 1) * 8;
     const int b_off = (lrow + (lmat >> 1) * 8) * kTStride + (lmat & 1) * 8;
+    const unsigned stage_at = (unsigned)__cvta_generic_to_shared(stage);
     stage_slice(0, 0);
     moe_cp_commit();
     const int n_slices = (ff + kTK - 1) / kTK;
@@ -415,8 +434,8 @@ __global__ void __launch_bounds__(128) moe_down_tc_kernel(const __nv_bfloat16* _
         moe_cp_commit();
         moe_cp_wait_all_but_one();
         __syncthreads();
-        const __nv_bfloat16* xs = stage + buf * 2 * kTile;
-        moe_warp_product(acc, xs + a_off, xs + kTile + b_off);
+        const unsigned xs = stage_at + buf * 2 * kTile * 2;
+        moe_warp_product(acc, xs + a_off * 2, xs + (kTile + b_off) * 2);
         __syncthreads();
     }
     const int p0 = first + warp * 16 + quad, p1 = p0 + 8;
