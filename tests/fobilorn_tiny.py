@@ -45,7 +45,16 @@ FOB_C = model(257, 72, 97, 1000003, 998244353, [
     layer(5, 5, 16, 12, 37, 0, None),
 ], eps=1e-6)
 
-CONFIGS = {"fob_a": FOB_A, "fob_b": FOB_B, "fob_c": FOB_C}
+# heads of 64 and of 128 lanes, the sizes the tensor-core kernels are mostly used with, values of 128 and of 72 lanes
+# (sixteen value tiles), groups of four and of one query head a kv head, windows shorter and longer than a page
+FOB_D = model(300, 128, 509, 7, 11, [
+    layer(4, 1, 64, 64, 100, 4, dense(192)),
+    layer(4, 2, 128, 128, 70, 0, moe(4, 2, 64, 64), v_mix=False),
+    layer(2, 2, 64, 72, 40, 65, None, v_mix=False),
+    layer(8, 1, 32, 64, 200, 1, moe(3, 1, 128)),
+])
+
+CONFIGS = {"fob_a": FOB_A, "fob_b": FOB_B, "fob_c": FOB_C, "fob_d": FOB_D}
 
 
 def make_folder(tmp_path, name, seed=0, dtype="bfloat16"):

@@ -140,7 +140,8 @@ def _append_and_attend(dtype, q, k, v, positions, block_table, n_pages, scale, w
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,dk,dv,window,keep", [(4, 2, 16, 8, 50, 3), (3, 3, 24, 40, 64, 0), (8, 1, 12, 12, 7, 66), (2, 1, 40, 260 // 10, 1000, 0)])
+@pytest.mark.parametrize("H,G,dk,dv,window,keep", [(4, 2, 16, 8, 50, 3), (3, 3, 24, 40, 64, 0), (8, 1, 12, 12, 7, 66), (2, 1, 40, 260 // 10, 1000, 0),
+                                                   (4, 2, 128, 128, 90, 5), (2, 2, 64, 72, 33, 0), (20, 1, 32, 32, 64, 64)])
 def test_attention_against_plain_in_prompts_and_token_by_token(dtype, H, G, dk, dv, window, keep):
     """A prompt in one step, the same in portions, then single tokens: windows and kept first tokens that cross pages,
     pages out of order, the sink, the gate."""
@@ -459,6 +460,35 @@ def test_greedy_generation_through_the_entry_point(tmp_path, name):
     hist = eng.decode_run(slots, first, 6).cpu().numpy()
     for i, res in enumerate(out.results[:2]):
         assert [first[i]] + hist[:-1, i].tolist() == list(res.tokens)[:6] or len(res.tokens) < 6
+
+
+def test_the_command_line_serves_the_design(tmp_path):
+    """`bin/burn-lm random --preset fobilorn_tiny` writes a folder, `bin/burn-lm run` generates from it in a child
+    process; the tokens are the plain implementation's greedy ones."""
+    import subprocess
+    import sys
+    program = [sys.executable, os.path.join(traces.ROOT, "bin", "burn-lm")]
+    folder = str(tmp_path / "f")
+    r = subprocess.run(program + ["random", folder, "--preset", "fobilorn_tiny", "--seed", "4", "--dtype", "bfloat16"],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and f"wrote {folder}" in r.stdout, r.stderr
+    cfg, tensors = P.read_model_folder(folder)
+    prompt = random_tokens(5, 23, cfg["vocab"])
+    r = subprocess.run(program + ["run", folder, "--dtype", "float32", "--sample-len", "10", "--max-seq-len", "128",
+                                  ",".join(map(str, prompt))], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr
+    got = [int(t) for t in [ln for ln in r.stdout.splitlines() if ln.strip()][0].split()]
+    seq = list(prompt)
+    for t in got:
+        logits = P.forward(cfg, tensors, seq)[-1]
+        order = np.argsort(logits)
+        if logits[order[-1]] - logits[order[-2]] < 1e-3 * np.abs(logits).max():
+            break                                        # a close call decides nothing
+        assert t == int(order[-1]), (len(seq) - len(prompt), t)
+        seq.append(t)
+    assert len(got) == 10 and len(seq) > len(prompt)
+    r = subprocess.run(program + ["models"], capture_output=True, text=True, timeout=300)
+    assert "Fobilorn" in r.stdout and "fobilorn_tiny" in r.stdout
 
 
 def test_trace_runner_chooses_the_model_by_its_configuration(tmp_path):
