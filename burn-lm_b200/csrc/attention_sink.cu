@@ -105,7 +105,7 @@ BLM_API int blm_qk_norm_append(const float* proj, long long proj_stride, int n_t
 // output) of its share of the keys and attention_sink_combine_kernel puts them together; the sink belongs to split 0.
 // ---------------------------------------------------------------------------------------------
 constexpr int kChunk = 32;
-constexpr int kMaxVRegs = 8;      // value lanes per thread: dv <= 32 * kMaxVRegs
+constexpr int kMaxVRegs = 16;     // value lanes per thread: dv <= 32 * kMaxVRegs
 
 // `count` consecutive elements of a cache row (count a multiple of the vector width where `vec`) to fp32
 template <typename T>

@@ -56,8 +56,8 @@ class SinkAttention(Part):
         super().__init__(spec, tensors, runtime)
         if spec.n_heads % spec.n_kv_heads:
             raise ValueError(f"{spec.n_heads} heads do not divide into {spec.n_kv_heads} kv heads")
-        if spec.value_dim > 256:
-            raise ValueError(f"value_dim {spec.value_dim}: the attention kernel takes values of up to 256 lanes")
+        if spec.value_dim > 512:
+            raise ValueError(f"value_dim {spec.value_dim}: the attention kernels take values of up to 512 lanes")
         if spec.value_blend not in (None, "source", "blend"):
             raise ValueError(f"value_blend is None, 'source' or 'blend', not {spec.value_blend!r}")
 
