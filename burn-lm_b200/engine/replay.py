@@ -56,6 +56,14 @@ class Replayer:
         return logits
 
 
+def cache_tokens(max_tokens: int) -> int:
+    """Token places of the cache for requests that hold up to `max_tokens` tokens together.  The cache hands out pages
+    of 64 positions and a request's last page is partly empty, so a count of tokens that does not round every request
+    up to a page needs some more: a page for each of 32 requests, or a quarter on top where that is more."""
+    from ..kernels import PAGE
+    return max_tokens + max(32 * PAGE, max_tokens // 4)
+
+
 def main(argv=None) -> int:
     import argparse
 
@@ -64,9 +72,10 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time, each rounded up to 64")
+                    help="most tokens live requests hold at any time; the cache is sized by it, with room for every "
+                         "request's last, partly filled page")
     args = ap.parse_args(argv)
-    engine = Engine.from_folder(args.model, dtype=args.dtype, max_tokens=args.max_tokens)
+    engine = Engine.from_folder(args.model, dtype=args.dtype, max_tokens=cache_tokens(args.max_tokens))
     rp = Replayer(engine, args.out)
     for line in sys.stdin:
         line = line.strip()

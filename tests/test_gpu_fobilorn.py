@@ -503,3 +503,15 @@ def test_trace_runner_chooses_the_model_by_its_configuration(tmp_path):
         want = P.forward(cfg, tensors, toks)
         for suffix in ("", "t", "b"):
             assert row_error(got[rid + suffix], want).max() < FP32_TOL, rid + suffix
+
+
+def test_trace_runner_has_room_for_partly_filled_pages(tmp_path):
+    """--max-tokens counts the tokens requests hold, not pages: requests of 1, 65 and 129 tokens together hold 195
+    tokens and six pages of 64 when no window lets pages go."""
+    folder = make_folder(tmp_path, "fob_b", seed=2, dtype="bfloat16")
+    cfg, tensors = P.read_model_folder(folder)
+    requests = {f"q{i}": random_tokens(70 + i, n, cfg["vocab"]) for i, n in enumerate([1, 65, 129])}
+    steps = traces.batched(requests, 3, [1, 4, 2])
+    got = traces.run_program(folder, "float32", steps, str(tmp_path / "o"), cfg["vocab"], max_tokens=195)
+    for rid, toks in requests.items():
+        assert row_error(got[rid], P.forward(cfg, tensors, toks)).max() < FP32_TOL, rid
