@@ -347,7 +347,11 @@ __device__ __forceinline__ void cp_async16(__nv_bfloat16* dst, const __nv_bfloat
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all_but_one() { asm volatile("cp.async.wait_group 1;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait_all_but() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+#ifndef BLM_PROMPT_STAGES
+#define BLM_PROMPT_STAGES 2
+#endif
+constexpr int kPromptStages = BLM_PROMPT_STAGES;       // pages of the prompt kernel in shared memory: one worked on, the others on their way
 
 // 2^x by the special function unit (the scores are in units of log 2; -inf gives 0)
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -417,22 +421,22 @@ __device__ __forceinline__ void stage_page(__nv_bfloat16* kbuf, __nv_bfloat16* v
     }
 }
 
-template <int NV>
-__global__ void __launch_bounds__(128) attention_sink_prompt_kernel(
+template <int NV, int HB>
+__global__ void __launch_bounds__(128 * HB) attention_sink_prompt_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pool, long long page_elems,
     const int* __restrict__ block_table, int table_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ start_pos,
     const int* __restrict__ slot_of_seq, int n_seqs, int n_tokens, const float* __restrict__ gate, long long gate_stride,
     __nv_bfloat16* __restrict__ out, int n_heads, int n_kv, int dk, int dv, int window, int keep_first, float scale, int sink) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __shared__ int found[3];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x, lane = tid & 31, warp = (tid >> 5) & 3, hb = tid >> 7;     // hb: which of the block's heads
     const int dkp = (dk + 15) & ~15;                   // the reduction runs in steps of 16 lanes; the rest is zeros
     const int qstride = dkp + 8;                       // rows 16 bytes apart modulo 128: ldmatrix reads eight of them at once
     constexpr int vstride = 8 * NV + 8;
-    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [64][qstride]
-    __nv_bfloat16* Kb = Qs + kTileQ * qstride;                           // 2 x [64][qstride]
-    __nv_bfloat16* Vb = Kb + 2 * kTileK * qstride;                       // 2 x [64][vstride]
-    const int head = blockIdx.y;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [HB][64][qstride]
+    __nv_bfloat16* Kb = Qs + HB * kTileQ * qstride;                      // kPromptStages x [64][qstride]
+    __nv_bfloat16* Vb = Kb + kPromptStages * kTileK * qstride;           // kPromptStages x [64][vstride]
+    const int head = blockIdx.y * HB + hb;             // the block's heads share a kv head (HB divides the group)
     if (tid == 0) {
         int t = blockIdx.x;
         found[0] = -1;
@@ -452,7 +456,7 @@ __global__ void __launch_bounds__(128) attention_sink_prompt_kernel(
     if (found[0] < 0) {
         // a block without a tile: the rows after the last sequence (padding up to a captured step's size) get zeros
         const int end = cu_seqlens[n_seqs];
-        for (int idx = tid; idx < (n_tokens - end) * dv; idx += blockDim.x)
+        for (int idx = tid & 127; idx < (n_tokens - end) * dv; idx += 128)
             out[((size_t)(end + idx / dv) * n_heads + head) * dv + idx % dv] = __float2bfloat16_rn(0.f);
         return;
     }
@@ -464,18 +468,26 @@ __global__ void __launch_bounds__(128) attention_sink_prompt_kernel(
     const int p_last = p0 + rows - 1;
     const int* pages = block_table + (size_t)slot_of_seq[seq] * table_stride;
     // zeros where no copy writes: rows of no query, lanes beyond dk and dv (the copies take whole groups of 8 lanes)
-    zero_unwritten(Qs, kTileQ, qstride, rows, dk);
-    zero_unwritten(Kb, 2 * kTileK, qstride, 2 * kTileK, dk);
-    zero_unwritten(Vb, 2 * kTileK, vstride, 2 * kTileK, dv);
+#pragma unroll
+    for (int i = 0; i < HB; ++i) zero_unwritten(Qs + i * kTileQ * qstride, kTileQ, qstride, rows, dk);
+    zero_unwritten(Kb, kPromptStages * kTileK, qstride, kPromptStages * kTileK, dk);
+    zero_unwritten(Vb, kPromptStages * kTileK, vstride, kPromptStages * kTileK, dv);
     const PageWalk walk(p0, p_last, window, keep_first);
-    for (int idx = tid; idx < rows * (dk / 8); idx += 128) {
+    for (int idx = tid & 127; idx < rows * (dk / 8); idx += 128) {       // every group of four warps brings its head's queries
         const int r = idx / (dk / 8), c = (idx % (dk / 8)) * 8;
-        cp_async16(Qs + r * qstride + c, q + ((size_t)(row0 + r) * n_heads + head) * dk + c, true);
+        cp_async16(Qs + (hb * kTileQ + r) * qstride + c, q + ((size_t)(row0 + r) * n_heads + head) * dk + c, true);
     }
     const GroupWalk kw(dk / 8), vw(dv / 8);
-    stage_page(Kb, Vb, pool + (size_t)pages[walk.page(0)] * page_elems, n_kv, kvh, dk, dv, qstride, vstride, walk.page(0) * kTileK, p_last,
-               kw, vw);
-    cp_async_commit();
+    auto fetch = [&](int it) {                         // page `it` of the walk into its place in the ring
+        const int pg = walk.page(it), b = it % kPromptStages;
+        stage_page(Kb + b * kTileK * qstride, Vb + b * kTileK * vstride, pool + (size_t)pages[pg] * page_elems, n_kv, kvh, dk, dv, qstride,
+                   vstride, pg * kTileK, p_last, kw, vw);
+    };
+#pragma unroll
+    for (int ahead = 0; ahead < kPromptStages - 1; ++ahead) {
+        if (ahead < walk.n_tiles) fetch(ahead);
+        cp_async_commit();
+    }
     const int quad = lane >> 2, pair = (lane & 3) * 2;
     const int lrow = lane & 7, lmat = lane >> 3;
     const int pr0 = p0 + warp * 16 + quad, pr1 = pr0 + 8;        // positions of this thread's two rows
@@ -485,19 +497,15 @@ __global__ void __launch_bounds__(128) attention_sink_prompt_kernel(
     l[0] = l[1] = sink ? 0.25f : 0.f;                  // a quad's four lanes add up to the sink's one
 #pragma unroll
     for (int j = 0; j < NV; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
-    const unsigned qa = smem_at(Qs + (warp * 16 + lrow + (lmat & 1) * 8) * qstride + (lmat >> 1) * 8);
+    const unsigned qa = smem_at(Qs + (hb * kTileQ + warp * 16 + lrow + (lmat & 1) * 8) * qstride + (lmat >> 1) * 8);
     const unsigned kb0 = smem_at(Kb + (lrow + (lmat >> 1) * 8) * qstride + (lmat & 1) * 8);
     const unsigned vb0 = smem_at(Vb + (lrow + (lmat & 1) * 8) * vstride + (lmat >> 1) * 8);
     const unsigned kstep = 16 * qstride * 2;           // bytes from 16 keys to the next 16
     for (int it = 0; it < walk.n_tiles; ++it) {
-        const int buf = it & 1;
-        if (it + 1 < walk.n_tiles) {
-            const int pg = walk.page(it + 1);
-            stage_page(Kb + (buf ^ 1) * kTileK * qstride, Vb + (buf ^ 1) * kTileK * vstride, pool + (size_t)pages[pg] * page_elems, n_kv, kvh,
-                       dk, dv, qstride, vstride, pg * kTileK, p_last, kw, vw);
-        }
+        const int buf = it % kPromptStages;
+        if (it + kPromptStages - 1 < walk.n_tiles) fetch(it + kPromptStages - 1);      // into the buffer the page before has left
         cp_async_commit();
-        cp_async_wait_all_but_one();                   // this tile (and the queries) have landed; the next may be on its way
+        cp_async_wait_all_but<kPromptStages - 1>();    // this page (and the queries) have landed; the others may be on their way
         __syncthreads();
         const int pg = walk.page(it);
         const unsigned kb = kb0 + buf * kTileK * qstride * 2, vb = vb0 + buf * kTileK * vstride * 2;
@@ -604,20 +612,20 @@ __global__ void __launch_bounds__(128) attention_sink_prompt_kernel(
     }
 }
 
-template <int NV>
+template <int NV, int HB>
 static int launch_prompt(const void* q, const void* pool, long long page_elems, const int* block_table, int table_stride,
                          const int* cu_seqlens, const int* start_pos, const int* slot_of_seq, int n_seqs, const float* gate,
                          long long gate_stride, void* out, int n_tokens, int n_heads, int n_kv, int dk, int dv, int window,
                          int keep_first, float scale, int sink, cudaStream_t stream) {
     const int dkp = (dk + 15) & ~15;
-    const size_t smem = ((size_t)3 * kTileQ * (dkp + 8) + (size_t)2 * kTileK * (8 * NV + 8)) * sizeof(__nv_bfloat16);
+    const size_t smem = ((size_t)(HB + kPromptStages) * kTileQ * (dkp + 8) + (size_t)kPromptStages * kTileK * (8 * NV + 8)) * sizeof(__nv_bfloat16);
     if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(attention_sink_prompt_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attention_sink_prompt_kernel<NV, HB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "attention_sink: %s", cudaGetErrorString(e));
     }
-    cudaFuncSetAttribute(attention_sink_prompt_kernel<NV>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(attention_sink_prompt_kernel<NV, HB>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     const unsigned tiles = (unsigned)((n_tokens + kTileQ - 1) / kTileQ + n_seqs);     // every sequence may end in a tile that is not full
-    attention_sink_prompt_kernel<NV><<<dim3(tiles, n_heads), 128, smem, stream>>>(
+    attention_sink_prompt_kernel<NV, HB><<<dim3(tiles, n_heads / HB), 128 * HB, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)pool, page_elems, block_table, table_stride, cu_seqlens, start_pos, slot_of_seq,
         n_seqs, n_tokens, gate, gate_stride, (__nv_bfloat16*)out, n_heads, n_kv, dk, dv, window, keep_first, scale, sink);
     return blm_check_launch("attention_sink (prompt)");
@@ -626,7 +634,6 @@ static int launch_prompt(const void* q, const void* pool, long long page_elems, 
 // kDecodeStages pages in shared memory, one worked on and the others on their way.  Measured with 64 sequences of
 // 1,088 tokens on 8 kv heads: heads of 64 lanes 45 us with two stages (five blocks to a multiprocessor), 60 with three,
 // 61 with four; heads of 128 lanes 84, 79 and 121 us.
-template <int N> __device__ __forceinline__ void cp_async_wait_all_but() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
 template <int NV, int kDecodeStages>
 __global__ void __launch_bounds__(128) attention_sink_decode_kernel(
@@ -829,6 +836,27 @@ static int launch_decode(const void* q, const void* pool, long long page_elems, 
     return blm_check_launch("attention_sink (decode)");
 }
 
+// How many query heads of a group share a block of the prompt kernel (and with it every page of keys and values that
+// the block brings in; the block's warps are four to a head), and how many pages it holds in shared memory (one worked
+// on, the others on their way).  Measured on one 2,048-token prompt, 32 heads on 8 kv heads, window 1,024, heads of 64
+// and of 128 lanes: one head and two pages 105 and 183 us; two heads 109 and 206; four heads 119 and 193; three
+// pages 109 and 275; four pages 133 and 270.  So one head and two pages it is; the others build with
+// -DBLM_PROMPT_HEADS=2|4 and -DBLM_PROMPT_STAGES=3|4.
+#ifndef BLM_PROMPT_HEADS
+#define BLM_PROMPT_HEADS 1
+#endif
+template <int NV, typename... Args>
+static int launch_prompt_heads(int hb, Args... args) {
+#if BLM_PROMPT_HEADS >= 4
+    if (hb == 4) return launch_prompt<NV, 4>(args...);
+#endif
+#if BLM_PROMPT_HEADS >= 2
+    if (hb >= 2) return launch_prompt<NV, 2>(args...);
+#endif
+    (void)hb;
+    return launch_prompt<NV, 1>(args...);
+}
+
 // Whether a step of this shape runs the prompt kernel (else the row kernel): bfloat16, pages of 64, sizes it takes,
 // and portions long enough to fill some of a tile's rows.
 BLM_API int blm_attention_sink_prompt_takes(int dtype, int dk, int dv, int page_size, int max_q_len, int n_heads) {
@@ -859,8 +887,11 @@ BLM_API int blm_attention_sink(const void* q, const void* pool, int dtype, long 
     BLM_REQUIRE(n_splits == 1 || partial != nullptr, "attention_sink: %d splits need scratch", n_splits);
     if (cu_seqlens != nullptr && start_pos != nullptr && n_seqs > 0 &&
         blm_attention_sink_prompt_takes(dtype, dk, dv, page_size, max_q_len, n_heads)) {
-#define BLM_PROMPT(NV) launch_prompt<NV>(q, pool, page_elems, block_table, table_stride, cu_seqlens, start_pos, slot_of_seq, n_seqs, gate, \
+#define BLM_PROMPT(NV) launch_prompt_heads<NV>(hb, q, pool, page_elems, block_table, table_stride, cu_seqlens, start_pos, slot_of_seq, n_seqs, gate, \
                                          gate_stride, out, n_tokens, n_heads, n_kv, dk, dv, window, keep_first, scale, sink, stream)
+        const int group = n_heads / n_kv;
+        int hb = BLM_PROMPT_HEADS;
+        while (hb > 1 && (group % hb != 0 || (hb == 4 && dv > 64))) hb /= 2;    // four heads of 128 lanes would not fit the registers
         if (dv <= 32) return BLM_PROMPT(4);
         if (dv <= 64) return BLM_PROMPT(8);
         return BLM_PROMPT(16);
