@@ -76,6 +76,8 @@ def fobilorn_plan(cfg: FobilornConfig) -> ModelPlan:
         final_norm=_norm(width, "final.norm"),
         head=PartPlan("linear", HeadSpec(cfg.vocab, width), {"weight": "head"}),
         max_positions=MAX_POSITIONS,
+        # a writer may store the blend's scalar in layers that do not blend; nothing reads it there
+        ignorable_tensors=(r"l\d+\.mix\.vmix",),
     )
 
 

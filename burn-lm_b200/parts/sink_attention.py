@@ -72,8 +72,8 @@ class SinkAttention(Part):
         if s.qk_norm_eps is not None:
             specs += [TensorSpec(t["q_norm"], (s.n_heads * s.head_dim,), init="one_plus_normal:0.1"),
                       TensorSpec(t["k_norm"], (s.n_kv_heads * s.head_dim,), init="one_plus_normal:0.1")]
-        if "blend" in t:
-            specs.append(TensorSpec(t["blend"], (), init="normal:0.3"))
+        if "blend" in t:       # the source layer's scalar is stored but unread
+            specs.append(TensorSpec(t["blend"], (), init="normal:0.3", optional=s.value_blend != "blend"))
         return specs
 
     def bind(self, loaded):

@@ -39,6 +39,8 @@ class TensorSpec:
     shape: tuple
     kind: str = "float"          # "float" or "int"
     init: str = "normal:0.02"    # for the random-weights mode: "normal:<std>" or "one_plus_normal:<std>"
+    optional: bool = False       # a tensor the format stores but the part does not read: loaded when it is there,
+                                 # not missed when it is not (the random-weights mode writes it)
 
 
 def _open_folder(folder: str) -> list[SafetensorsFile]:
@@ -82,7 +84,7 @@ def load_tensors(folder: str, specs: list, compute_dtype: torch.dtype, device, i
                 raise WeightsError(f"tensor {s.name!r} is asked for with two shapes: "
                                    f"{wanted[s.name].shape} and {tuple(s.shape)}")
             wanted[s.name] = s
-        missing = [n for n in wanted if n not in where]
+        missing = [n for n in wanted if n not in where and not wanted[n].optional]
         patterns = [re.compile(p) for p in ignorable]
         copies = {a: b for a, b in duplicates if a in where and a not in wanted and b in where}
         unexpected = [n for n in where if n not in wanted and n not in copies and not any(p.fullmatch(n) for p in patterns)]
@@ -114,6 +116,8 @@ def load_tensors(folder: str, specs: list, compute_dtype: torch.dtype, device, i
             raise WeightsError("\n".join(lines), missing, unexpected, wrong, differing)
         out = {}
         for n, s in wanted.items():
+            if n not in where:
+                continue            # optional and absent
             f = where[n]
             t = f.get(n)
             out[n] = t.to(device=device, dtype=_target_dtype(t.dtype, s.kind, compute_dtype), copy=True)

@@ -126,3 +126,23 @@ def test_plain_mechanisms():
     # routing: the largest scores, the lower index first on a tie, weights not renormalised
     ids, w = P.route(np.array([[1.0, 0.0]]), np.array([[2.0, 0.0], [2.0, 0.0], [-1.0, 0.0], [3.0, 0.0]]), 3)
     assert ids.tolist() == [[3, 0, 1]] and abs(w.sum() - (P.sigmoid(3.0) + 2 * P.sigmoid(2.0))) < 1e-12
+
+
+def test_a_blend_scalar_stored_in_a_layer_that_does_not_blend_is_left_unread(tmp_path):
+    import torch
+    from safetensors.torch import load_file, save_file
+    from burn_lm_b200.weights.loader import load_tensors
+    folder = make_folder(tmp_path, "fob_a", seed=3)
+    path = os.path.join(folder, "model.safetensors")
+    tensors = load_file(path)
+    assert "l1.mix.vmix" not in tensors                       # layer 1 of this configuration does not blend
+    tensors["l1.mix.vmix"] = torch.tensor(0.25, dtype=torch.bfloat16)
+    save_file(tensors, path)
+    _, _, plan = plan_of(copy.deepcopy(FOB_A))
+    got = load_tensors(folder, tensor_specs_of(FOB_A), torch.float32, "cpu", plan.ignorable_tensors)
+    assert "l1.mix.vmix" not in got and "l0.mix.vmix" in got
+    # and the source layer's scalar, which nothing reads, may be absent
+    del tensors["l0.mix.vmix"], tensors["l1.mix.vmix"]
+    save_file(tensors, path)
+    got = load_tensors(folder, tensor_specs_of(FOB_A), torch.float32, "cpu", plan.ignorable_tensors)
+    assert "l0.mix.vmix" not in got and "l2.mix.vmix" in got
