@@ -9,7 +9,6 @@ heads, G key/value heads, dk the query/key size of a head and dv its value size.
 from __future__ import annotations
 
 import json
-import math
 import os
 
 import numpy as np

@@ -1,7 +1,6 @@
 """What needs no GPU of the Fobilorn decoder: its configuration reader, its plan and tensor list, the registry, the
 cache's kept first pages and paged lines of ids, and the plain implementation's own mechanisms."""
 import copy
-import json
 import os
 
 import numpy as np
