@@ -1,3 +1,4 @@
 """Architectures this package knows; importing registers them."""
 from . import llama  # noqa: F401
 from . import fobilorn  # noqa: F401
+from . import nufolix  # noqa: F401

@@ -107,8 +107,13 @@ class Cache:
         self._state_groups: list[_StateGroup] = []
         self._where: dict[int, tuple] = {}      # run -> ("kv" | "state" | "none", group, index in group)
         by_need: dict = {}
+        several: dict[int, int] = {}            # run -> how many needs it has, when its mixer keeps several things
         for run, need in enumerate(needs):
-            if need is not None:
+            if isinstance(need, tuple):
+                several[run] = len(need)
+                for j, one in enumerate(need):
+                    by_need.setdefault(one, []).append((run, j))
+            elif need is not None:
                 by_need.setdefault(need, []).append(run)
         for name, need in (named or {}).items():
             by_need.setdefault(need, []).append(("named", name))
@@ -133,8 +138,11 @@ class Cache:
         self._views = []
         for run, entry in enumerate(schedule):
             src = run if entry.cache_of is None else entry.cache_of
-            kind, g, i = self._where[src]
             writes = entry.cache_of is None
+            if src in several:
+                self._views.append(self._merged([self._view_of(*self._where[(src, j)], writes) for j in range(several[src])]))
+                continue
+            kind, g, i = self._where[src]
             self._views.append(self._view_of(kind, g, i, writes))
         self._named_views = {name: self._view_of(*self._where[("named", name)], True) for name in (named or {})}
 
@@ -146,6 +154,21 @@ class Cache:
         if kind == "state":
             return CacheView("state", writes, state=g.state[i])
         return CacheView("none", writes)
+
+    @staticmethod
+    def _merged(views):
+        """One view of a run whose mixer keeps several things (keys and values beside a state, say): at most one of
+        each kind; the fields of both are filled and `kind` names them joined by '+'."""
+        kinds = [v.kind for v in views if v.kind != "none"]
+        if len(set(kinds)) != len(kinds):
+            raise CacheError(f"a run keeps two things of one kind: {kinds}")
+        out = CacheView("+".join(kinds) if kinds else "none", views[0].writes)
+        for v in views:
+            if v.kind in ("kv", "ids"):
+                out.pool, out.block_table, out.window, out.keep_first = v.pool, v.block_table, v.window, v.keep_first
+            elif v.kind == "state":
+                out.state = v.state
+        return out
 
     # -- what the model sees -------------------------------------------------------------------------
     def view(self, run: int) -> CacheView:

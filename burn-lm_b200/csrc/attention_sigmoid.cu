@@ -1,0 +1,355 @@
+// Causal attention without a softmax, with the heads' weights mixed before they meet the values:
+//     s_h(i, j) = scale q_hi . k_cj (c the key/value head of h), optionally capped: cap tanh(s / cap)
+//     w_h(i, j) = sigmoid(s_h(i, j) + bias_h) for j <= i, else 0          (not normalised over the keys)
+//     m_h(i, j) = sum_g talk[h, g] w_g(i, j)                              (talk null: m = w)
+//     out_h(i)  = sum_j m_h(i, j) v_cj
+// and the kernel in front of it: projection bias, rotation of the first `rot` lanes of every q and k head (lane i
+// with lane i + rot / 2, angle = position * freq[i] in fp32), append of k and v to the paged cache.
+// Scores, weights, the mix and the sums over keys are fp32 in both dtypes.
+//
+// Because nothing normalises over the keys, a query's keys can be cut into ranges whose partial outputs simply add:
+// grid.y blocks take a range each and a second kernel adds the ranges in order.  A block owns BQ query rows of one
+// sequence with ALL heads (the mix needs every head's weight at a key), walks its keys a chunk of a cache page at a
+// time: scores of all heads, mix, then the values; outputs are kept in registers.
+#include "common.cuh"
+
+BLM_API const char* blm_attention_sigmoid_last_error() { return g_blm_error; }
+
+constexpr int kThreads = 256;
+
+// ---------------------------------------------------------------------------------------------
+// bias + rotation + append
+//   proj fp32 [N, stride]: q heads (H x dk), k heads (G x dk), v heads (G x dv); bias [that width] or null
+//   q_out [N, H dk]; a cache page: keys [G][page][dk] then values [G][page][dv]
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void bias_rope_append_kernel(const float* __restrict__ proj, long long stride, const float* __restrict__ bias,
+                                        const float* __restrict__ freq, int rot, T* __restrict__ q_out, T* __restrict__ pool,
+                                        const int* __restrict__ token_seq, const int* __restrict__ token_pos,
+                                        const int* __restrict__ slot_of_seq, const int* __restrict__ block_table, int table_stride,
+                                        int H, int G, int dk, int dv, int page) {
+    const int n = blockIdx.y;
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    const int qk = (H + G) * dk;
+    const int width = qk + G * dv;
+    if (e >= width) return;
+    const float* row = proj + (size_t)n * stride;
+    const int pos = token_pos[n];
+    float val = row[e] + (bias ? bias[e] : 0.f);
+    int head = 0, lane = 0;
+    if (e < qk) {
+        head = e / dk;
+        lane = e % dk;
+        if (lane < rot) {
+            const int half = rot >> 1;
+            const int i = lane < half ? lane : lane - half;
+            const int pe = lane < half ? e + half : e - half;
+            const float other = row[pe] + (bias ? bias[pe] : 0.f);
+            float s, c;
+            sincosf((float)pos * freq[i], &s, &c);
+            val = lane < half ? val * c - other * s : val * c + other * s;
+        }
+        if (head < H) {
+            q_out[(size_t)n * H * dk + e] = from_f32<T>(val);
+            return;
+        }
+        head -= H;
+    } else {
+        head = (e - qk) / dv;
+        lane = (e - qk) % dv;
+    }
+    const int seq = token_seq[n];
+    if (seq < 0) return;             // a row of no sequence: nothing of it reaches the cache
+    const int pg = block_table[(size_t)slot_of_seq[seq] * table_stride + pos / page];
+    T* base = pool + (size_t)pg * G * page * (dk + dv);
+    const int at = pos % page;
+    if (e < qk) base[((size_t)head * page + at) * dk + lane] = from_f32<T>(val);
+    else base[(size_t)G * page * dk + ((size_t)head * page + at) * dv + lane] = from_f32<T>(val);
+}
+
+BLM_API int blm_bias_rope_append(const float* proj, long long stride, const float* bias, const float* freq, int rot, void* q_out,
+                                 void* pool, int dtype, const int* token_seq, const int* token_pos, const int* slot_of_seq,
+                                 const int* block_table, int table_stride, int n, int H, int G, int dk, int dv, int page,
+                                 cudaStream_t stream) {
+    if (n == 0) return BLM_OK;
+    BLM_REQUIRE(H > 0 && G > 0 && dk > 0 && dv > 0 && page > 0, "bias_rope_append: bad sizes");
+    BLM_REQUIRE(rot >= 0 && rot <= dk && rot % 2 == 0 && (rot == 0 || freq != nullptr), "bias_rope_append: %d rotated lanes of %d", rot, dk);
+    BLM_REQUIRE(n <= 65535 * 64, "bias_rope_append: too many rows");
+    const int width = (H + G) * dk + G * dv;
+    dim3 grid((width + 255) / 256, n);
+    if (dtype == BLM_F32)
+        bias_rope_append_kernel<float><<<grid, 256, 0, stream>>>(proj, stride, bias, freq, rot, (float*)q_out, (float*)pool, token_seq,
+                                                                 token_pos, slot_of_seq, block_table, table_stride, H, G, dk, dv, page);
+    else if (dtype == BLM_BF16)
+        bias_rope_append_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(proj, stride, bias, freq, rot, (__nv_bfloat16*)q_out,
+                                                                         (__nv_bfloat16*)pool, token_seq, token_pos, slot_of_seq,
+                                                                         block_table, table_stride, H, G, dk, dv, page);
+    else
+        return blm_fail(BLM_BAD_ARGUMENT, "bias_rope_append: dtype %d", dtype);
+    return blm_check_launch("bias_rope_append");
+}
+
+// ---------------------------------------------------------------------------------------------
+// the attention
+// ---------------------------------------------------------------------------------------------
+template <typename T> struct Vec;
+template <> struct Vec<float> { static constexpr int n = 4; };
+template <> struct Vec<__nv_bfloat16> { static constexpr int n = 8; };
+
+// rows are padded to a multiple of a 16-byte vector, plus one vector so that rows start in different banks
+template <typename T> __host__ __device__ inline int padded(int d) { return (d + Vec<T>::n - 1) / Vec<T>::n * Vec<T>::n + Vec<T>::n; }
+
+__device__ __forceinline__ float dot16(const float* a, const float* b, int n) {
+    float acc = 0.f;
+    for (int i = 0; i < n; i += 4) {
+        const float4 x = *reinterpret_cast<const float4*>(a + i), y = *reinterpret_cast<const float4*>(b + i);
+        acc += x.x * y.x;
+        acc += x.y * y.y;
+        acc += x.z * y.z;
+        acc += x.w * y.w;
+    }
+    return acc;
+}
+__device__ __forceinline__ float dot16(const __nv_bfloat16* a, const __nv_bfloat16* b, int n) {
+    float acc = 0.f;
+    for (int i = 0; i < n; i += 8) {
+        const uint4 x = *reinterpret_cast<const uint4*>(a + i), y = *reinterpret_cast<const uint4*>(b + i);
+        const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&x);
+        const __nv_bfloat162* yp = reinterpret_cast<const __nv_bfloat162*>(&y);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(xp[e]), g = __bfloat1622float2(yp[e]);
+            acc += f.x * g.x;
+            acc += f.y * g.y;
+        }
+    }
+    return acc;
+}
+
+struct SigmoidAttnArgs {
+    const void* q;            // [N, H dk]
+    const void* pool;         // pages: keys [G][page][dk] then values [G][page][dv]
+    const int* block_table;
+    int table_stride;
+    const int* cu_seqlens;
+    const int* slot_of_seq;
+    const int* start_pos;
+    const float* talk;        // [H, H] or null
+    const float* head_bias;   // [H] or null
+    void* out;                // [N, H dv] in the activation dtype (one range)
+    float* partial;           // [ranges][N][H dv] fp32 (several ranges)
+    int n_tokens, n_seqs, q_tiles, H, G, dk, dv, page, BQ, KC, ranges;
+    float scale, softcap;
+};
+
+template <typename T, int ACC>
+__global__ void __launch_bounds__(kThreads) sigmoid_attn_kernel(const SigmoidAttnArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int H = a.H, G = a.G, dk = a.dk, dv = a.dv, BQ = a.BQ, KC = a.KC;
+    const int dkp = padded<T>(dk), dvp = padded<T>(dv);
+    float* Ts = reinterpret_cast<float*>(smem_raw);                 // [H][H]
+    float* pbs = Ts + (H * H + 3) / 4 * 4;                           // [H]
+    float* Ss = pbs + ((H + 3) / 4) * 4;                             // [H][BQ][KC]
+    float* Ms = Ss + H * BQ * KC;                                    // [H][BQ][KC]
+    T* Qs = reinterpret_cast<T*>(Ms + H * BQ * KC);                  // [H][BQ][dkp]
+    T* KVs = Qs + (size_t)H * BQ * dkp;                              // [G][KC][kvp]
+    const int tid = threadIdx.x;
+    const int seq = blockIdx.x / a.q_tiles, tile = blockIdx.x % a.q_tiles;
+    const int first = a.cu_seqlens[seq];
+    const int n_new = a.cu_seqlens[seq + 1] - first;
+    const int i0 = tile * BQ;
+    if (i0 >= n_new) return;
+    const int nq = min(BQ, n_new - i0);
+    const int start = a.start_pos[seq];
+    const int kv_hi = start + i0 + nq;                  // keys 0 .. kv_hi - 1 are seen by some row of the tile
+    const int chunks = (kv_hi + KC - 1) / KC;
+    const int per = (chunks + a.ranges - 1) / a.ranges;
+    const int c_lo = blockIdx.y * per, c_hi = min(chunks, c_lo + per);
+    const int* table = a.block_table + (size_t)a.slot_of_seq[seq] * a.table_stride;
+    const int per_kv = H / G;
+    const int HD = H * dv;
+
+    for (int e = tid; e < H * H; e += kThreads) Ts[e] = a.talk ? a.talk[e] : (e / H == e % H ? 1.f : 0.f);
+    for (int e = tid; e < H; e += kThreads) pbs[e] = a.head_bias ? a.head_bias[e] : 0.f;
+    // the tile's queries, rows beyond the tile and lanes beyond dk as zeros
+    const T* q = reinterpret_cast<const T*>(a.q);
+    for (int e = tid; e < H * BQ * dkp; e += kThreads) {
+        const int l = e % dkp, i = (e / dkp) % BQ, h = e / (dkp * BQ);
+        Qs[e] = (l < dk && i < nq) ? q[(size_t)(first + i0 + i) * H * dk + h * dk + l] : from_f32<T>(0.f);
+    }
+    float acc[ACC];
+#pragma unroll
+    for (int x = 0; x < ACC; ++x) acc[x] = 0.f;
+    const int n_out = H * BQ * dv;                       // output e = (h, i, p), p fastest; thread tid owns e = tid + x * kThreads
+    const T* pool = reinterpret_cast<const T*>(a.pool);
+    const size_t page_elems = (size_t)G * a.page * (dk + dv);
+    const bool cap = a.softcap > 0.f;
+    const float inv_cap = cap ? 1.0f / a.softcap : 0.f;
+
+    for (int ch = c_lo; ch < c_hi; ++ch) {
+        const int j0 = ch * KC;
+        const T* pg = pool + (size_t)table[j0 / a.page] * page_elems;
+        const int at0 = j0 % a.page;
+        __syncthreads();                                  // the chunk before is done with KVs, Ss and Ms
+        for (int e = tid; e < G * KC * dkp; e += kThreads) {
+            const int l = e % dkp, j = (e / dkp) % KC, g = e / (dkp * KC);
+            KVs[e] = (l < dk && j0 + j < kv_hi) ? pg[((size_t)g * a.page + at0 + j) * dk + l] : from_f32<T>(0.f);
+        }
+        __syncthreads();
+        // scores and weights of all heads
+        for (int e = tid; e < H * BQ * KC; e += kThreads) {
+            const int j = e % KC, i = (e / KC) % BQ, h = e / (KC * BQ);
+            float w = 0.f;
+            if (i < nq && j0 + j <= start + i0 + i) {
+                float s = dot16(Qs + (size_t)(h * BQ + i) * dkp, KVs + (size_t)((h / per_kv) * KC + j) * dkp, dkp - Vec<T>::n) * a.scale;
+                if (cap) s = a.softcap * tanhf(s * inv_cap);
+                w = 1.0f / (1.0f + expf(-(s + pbs[h])));
+            }
+            Ss[e] = w;
+        }
+        __syncthreads();
+        // the values take the keys' place while the weights are mixed
+        for (int e = tid; e < G * KC * dvp; e += kThreads) {
+            const int l = e % dvp, j = (e / dvp) % KC, g = e / (dvp * KC);
+            KVs[e] = (l < dv && j0 + j < kv_hi)
+                         ? pg[(size_t)G * a.page * dk + ((size_t)g * a.page + at0 + j) * dv + l] : from_f32<T>(0.f);
+        }
+        const int ij = BQ * KC;
+        for (int e = tid; e < H * ij; e += kThreads) {
+            const int x = e % ij, h = e / ij;
+            const float* t = Ts + h * H;
+            float m = 0.f;
+            for (int g = 0; g < H; ++g) m += t[g] * Ss[g * ij + x];
+            Ms[e] = m;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int x = 0; x < ACC; ++x) {
+            const int e = tid + x * kThreads;
+            if (e < n_out) {
+                const int p = e % dv, i = (e / dv) % BQ, h = e / (dv * BQ);
+                const float* m = Ms + (size_t)(h * BQ + i) * KC;
+                const T* v = KVs + (size_t)((h / per_kv) * KC) * dvp + p;
+                float s = acc[x];
+                for (int j = 0; j < KC; ++j) s += m[j] * to_f32(v[(size_t)j * dvp]);
+                acc[x] = s;
+            }
+        }
+    }
+#pragma unroll
+    for (int x = 0; x < ACC; ++x) {
+        const int e = tid + x * kThreads;
+        if (e < n_out) {
+            const int p = e % dv, i = (e / dv) % BQ, h = e / (dv * BQ);
+            if (i < nq) {
+                const size_t at = (size_t)(first + i0 + i) * HD + h * dv + p;
+                if (a.ranges > 1) a.partial[(size_t)blockIdx.y * a.n_tokens * HD + at] = acc[x];
+                else reinterpret_cast<T*>(a.out)[at] = from_f32<T>(acc[x]);
+            }
+        }
+    }
+}
+
+// out[n, :] = the ranges' partial outputs added in order; rows of no sequence get zeros
+template <typename T>
+__global__ void add_ranges_kernel(const float* __restrict__ partial, T* __restrict__ out, const int* __restrict__ token_seq,
+                                  int n_tokens, int HD, int ranges) {
+    const int n = blockIdx.y;
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= HD) return;
+    float s = 0.f;
+    if (token_seq[n] >= 0)
+        for (int r = 0; r < ranges; ++r) s += partial[((size_t)r * n_tokens + n) * HD + e];
+    out[(size_t)n * HD + e] = from_f32<T>(s);
+}
+
+struct SigmoidAttnPlan {
+    int BQ, KC, acc;
+    size_t smem;
+};
+
+template <typename T>
+static size_t smem_bytes(int H, int G, int dk, int dv, int BQ, int KC) {
+    const int dkp = padded<T>(dk), dvp = padded<T>(dv), kvp = dkp > dvp ? dkp : dvp;
+    return ((size_t)(H * H + 3) / 4 * 4 + (H + 3) / 4 * 4 + 2 * (size_t)H * BQ * KC) * sizeof(float) +
+           ((size_t)H * BQ * dkp + (size_t)G * KC * kvp) * sizeof(T);
+}
+
+// BQ: as many query rows as the registers hold outputs for (64 a thread at most), 8 at most, no more than the step
+// has; KC: 64, 32 or 16 keys, the most that fits the shared memory.
+template <typename T>
+static bool plan_for(int H, int G, int dk, int dv, int max_q_len, int page, SigmoidAttnPlan* p) {
+    const size_t limit = 200 * 1024;
+    int BQ = 8;
+    while (BQ > 1 && ((size_t)H * BQ * dv > (size_t)64 * kThreads || BQ / 2 >= max_q_len)) BQ /= 2;
+    if ((size_t)H * BQ * dv > (size_t)64 * kThreads) return false;
+    for (; BQ >= 1; BQ /= 2) {
+        for (int KC = 64; KC >= 16; KC /= 2) {
+            if (KC > page || page % KC) continue;
+            const size_t s = smem_bytes<T>(H, G, dk, dv, BQ, KC);
+            if (s <= limit) {
+                const size_t outs = ((size_t)H * BQ * dv + kThreads - 1) / kThreads;
+                p->BQ = BQ;
+                p->KC = KC;
+                p->acc = outs <= 4 ? 4 : (outs <= 16 ? 16 : 64);
+                p->smem = s;
+                return true;
+            }
+        }
+    }
+    return false;
+}
+
+BLM_API int blm_sigmoid_attention_takes(int dtype, int H, int G, int dk, int dv, int page) {
+    SigmoidAttnPlan p;
+    if (H < 1 || G < 1 || H % G) return 0;
+    return dtype == BLM_F32 ? plan_for<float>(H, G, dk, dv, 1, page, &p) : plan_for<__nv_bfloat16>(H, G, dk, dv, 1, page, &p);
+}
+
+template <typename T>
+static int launch_sigmoid_attention(SigmoidAttnArgs a, int max_q_len, const int* token_seq, cudaStream_t stream) {
+    SigmoidAttnPlan p;
+    BLM_REQUIRE(plan_for<T>(a.H, a.G, a.dk, a.dv, max_q_len, a.page, &p),
+                "sigmoid_attention: %d heads of %d + %d lanes do not fit this kernel's registers and shared memory", a.H, a.dk, a.dv);
+    a.BQ = p.BQ;
+    a.KC = p.KC;
+    a.q_tiles = (max_q_len + p.BQ - 1) / p.BQ;
+    BLM_REQUIRE((long long)a.n_seqs * a.q_tiles <= 0x7fffffffLL && a.ranges <= 65535, "sigmoid_attention: grid too large");
+    dim3 grid(a.n_seqs * a.q_tiles, a.ranges);
+#define BLM_SA(ACC)                                                                                                      \
+    {                                                                                                                    \
+        auto k = sigmoid_attn_kernel<T, ACC>;                                                                            \
+        if (p.smem > 48 * 1024) {                                                                                        \
+            cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)p.smem);           \
+            if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "sigmoid_attention: %s", cudaGetErrorString(e));       \
+        }                                                                                                                \
+        k<<<grid, kThreads, p.smem, stream>>>(a);                                                                        \
+    }
+    if (p.acc == 4) BLM_SA(4) else if (p.acc == 16) BLM_SA(16) else BLM_SA(64)
+#undef BLM_SA
+    int rc = blm_check_launch("sigmoid_attention");
+    if (rc != BLM_OK || a.ranges == 1) return rc;
+    const int HD = a.H * a.dv;
+    dim3 grid2((HD + 255) / 256, a.n_tokens);
+    add_ranges_kernel<T><<<grid2, 256, 0, stream>>>(a.partial, (T*)a.out, token_seq, a.n_tokens, HD, a.ranges);
+    return blm_check_launch("sigmoid_attention (ranges)");
+}
+
+BLM_API int blm_sigmoid_attention(const void* q, const void* pool, int dtype, const int* block_table, int table_stride,
+                                  const int* cu_seqlens, const int* slot_of_seq, const int* start_pos, const int* token_seq,
+                                  const float* talk, const float* head_bias, void* out, float* partial, int n_tokens, int n_seqs,
+                                  int max_q_len, int H, int G, int dk, int dv, int page, int ranges, float scale, float softcap,
+                                  cudaStream_t stream) {
+    if (n_tokens == 0 || n_seqs == 0) return BLM_OK;
+    BLM_REQUIRE(H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0 && max_q_len > 0, "sigmoid_attention: bad sizes");
+    BLM_REQUIRE(ranges >= 1 && (ranges == 1 || partial != nullptr), "sigmoid_attention: several key ranges need a workspace");
+    BLM_REQUIRE(n_tokens <= 65535 * 64, "sigmoid_attention: too many rows");
+    SigmoidAttnArgs a;
+    a.q = q; a.pool = pool; a.block_table = block_table; a.table_stride = table_stride; a.cu_seqlens = cu_seqlens;
+    a.slot_of_seq = slot_of_seq; a.start_pos = start_pos; a.talk = talk; a.head_bias = head_bias; a.out = out; a.partial = partial;
+    a.n_tokens = n_tokens; a.n_seqs = n_seqs; a.q_tiles = 0; a.H = H; a.G = G; a.dk = dk; a.dv = dv; a.page = page; a.BQ = 0; a.KC = 0;
+    a.ranges = ranges; a.scale = scale; a.softcap = softcap;
+    if (dtype == BLM_F32) return launch_sigmoid_attention<float>(a, max_q_len, token_seq, stream);
+    if (dtype == BLM_BF16) return launch_sigmoid_attention<__nv_bfloat16>(a, max_q_len, token_seq, stream);
+    return blm_fail(BLM_BAD_ARGUMENT, "sigmoid_attention: dtype %d", dtype);
+}

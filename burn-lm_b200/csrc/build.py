@@ -34,6 +34,9 @@ MODULES = {
     "attention": ["attention.cu"],
     "attention_sink": ["attention_sink.cu"],
     "moe": ["moe.cu"],
+    "stream_ops": ["stream_ops.cu"],
+    "recurrent": ["recurrent.cu"],
+    "attention_sigmoid": ["attention_sigmoid.cu"],
     "gemm": ["gemm_f32.cu"],
     "gemv": ["gemv.cu"],
     "gemm_tc": ["gemm_tc.cu"],

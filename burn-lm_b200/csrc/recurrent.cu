@@ -1,0 +1,435 @@
+// Recurrent mixers over the packed tokens of a step: the short causal convolution with its carried inputs, the
+// state-space scan (a scalar decay per head), the gated delta rule (a decay per key channel, an error-correcting
+// write), and the group-wise RMS norm with a gate that follows either.  Everything here is fp32.
+//
+// What a sequence carries lives in a fixed-size block per cache slot, twice: a step that starts at position p reads
+// copy (p & 1) and writes copy ((p + n) & 1) for its n new tokens.  A single-token step therefore never overwrites
+// what it read, and running it again (a warm-up before a captured graph, a step enqueued ahead and then forgotten)
+// gives the same result.  A step that starts at position 0 reads zeros whatever the block holds.
+//
+// A scan block owns (sequence, head, 32 value columns): 256 threads = 32 columns x 8 row groups; thread (col, rg) keeps
+// rows rg, rg + 8, rg + 16, ... of its column in registers.  A sum over rows is a thread's partial sum and then three
+// shuffles over the eight row groups: the same order whatever the step's size or batch.  The state is stored as
+// [head][row / 8][column][row % 8], which is the order in which a warp holds it.
+#include "common.cuh"
+
+BLM_API const char* blm_recurrent_last_error() { return g_blm_error; }
+
+constexpr int kMaxTaps = 8;
+constexpr int kCols = 32;          // value columns a scan block owns
+constexpr int kRowGroups = 8;
+constexpr int kChunk = 32;         // tokens staged in shared memory at a time
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
+__device__ __forceinline__ float sigmoid_f(float v) { return 1.0f / (1.0f + expf(-v)); }
+__device__ __forceinline__ float softplus_r(float v) { return fmaxf(v, 0.f) + log1pf(expf(-fabsf(v))); }
+
+// ---------------------------------------------------------------------------------------------
+// causal convolution per channel over time, then optionally silu
+//   x [N, x_stride] (channels at x_col0 ..), taps [C, K] (the last column is the current token's), bias [C] or null
+//   carried inputs: hist [K - 1][C] per copy, hist[m] = the input at position start - (K - 1) + m
+// ---------------------------------------------------------------------------------------------
+__global__ void conv_kernel(const float* __restrict__ x, long long x_stride, int x_col0, int channels,
+                            const float* __restrict__ taps, const float* __restrict__ bias, int K, int act,
+                            float* __restrict__ out, long long out_stride, int out_col0,
+                            const int* __restrict__ token_seq, const int* __restrict__ cu_seqlens,
+                            const int* __restrict__ slot_of_seq, const int* __restrict__ start_pos,
+                            const float* __restrict__ state, long long slot_stride, long long copy_stride, long long hist_off) {
+    const int n = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    float* o = out + (size_t)n * out_stride + out_col0 + c;
+    const int seq = token_seq[n];
+    if (seq < 0) {           // a row of no sequence
+        *o = 0.f;
+        return;
+    }
+    const int i = n - cu_seqlens[seq];
+    const int start = start_pos[seq];
+    const float* hist = state + (size_t)slot_of_seq[seq] * slot_stride + (size_t)(start & 1) * copy_stride + hist_off;
+    float acc = bias ? bias[c] : 0.f;
+    for (int j = K - 1; j >= 0; --j) {          // the oldest input first
+        const int back = i - j;                   // index among the step's rows of this sequence
+        float v;
+        if (back >= 0) v = x[(size_t)(n - j) * x_stride + x_col0 + c];
+        else if (start + back < 0) v = 0.f;
+        else v = hist[(size_t)(K - 1 + back) * channels + c];
+        acc += taps[(size_t)c * K + (K - 1 - j)] * v;
+    }
+    *o = act ? silu_f(acc) : acc;
+}
+
+__global__ void conv_carry_kernel(const float* __restrict__ x, long long x_stride, int x_col0, int channels, int K,
+                                  const int* __restrict__ cu_seqlens, const int* __restrict__ slot_of_seq,
+                                  const int* __restrict__ start_pos, float* __restrict__ state, long long slot_stride,
+                                  long long copy_stride, long long hist_off) {
+    const int seq = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    const int first = cu_seqlens[seq];
+    const int n_new = cu_seqlens[seq + 1] - first;
+    if (n_new <= 0) return;      // an empty sequence (padding of a captured step)
+    const int start = start_pos[seq];
+    float* base = state + (size_t)slot_of_seq[seq] * slot_stride + hist_off;
+    const float* old = base + (size_t)(start & 1) * copy_stride;
+    float* fresh = base + (size_t)((start + n_new) & 1) * copy_stride;
+    float keep[kMaxTaps];
+#pragma unroll
+    for (int m = 0; m < kMaxTaps - 1; ++m) {
+        if (m < K - 1) {
+            const int p = start + n_new - (K - 1) + m;      // the position whose input goes to place m
+            float v;
+            if (p < 0) v = 0.f;
+            else if (p >= start) v = x[(size_t)(first + (p - start)) * x_stride + x_col0 + c];
+            else v = old[(size_t)(K - 1 + (p - start)) * channels + c];
+            keep[m] = v;
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < kMaxTaps - 1; ++m)
+        if (m < K - 1) fresh[(size_t)m * channels + c] = keep[m];
+}
+
+BLM_API int blm_causal_conv(const float* x, long long x_stride, int x_col0, int channels, const float* taps, const float* bias,
+                            int K, int act, float* out, long long out_stride, int out_col0, const int* token_seq,
+                            const int* cu_seqlens, const int* slot_of_seq, const int* start_pos, int n_tokens, int n_seqs,
+                            float* state, long long slot_stride, long long copy_stride, long long hist_off,
+                            cudaStream_t stream) {
+    if (n_tokens == 0) return BLM_OK;
+    BLM_REQUIRE(channels > 0 && K >= 1 && K <= kMaxTaps, "causal_conv: %d taps; this kernel takes 1 to %d", K, kMaxTaps);
+    BLM_REQUIRE(n_tokens <= 65535 * 64 && n_seqs <= 65535, "causal_conv: too many rows");
+    const int threads = 128;
+    dim3 grid((channels + threads - 1) / threads, n_tokens);
+    conv_kernel<<<grid, threads, 0, stream>>>(x, x_stride, x_col0, channels, taps, bias, K, act, out, out_stride, out_col0,
+                                              token_seq, cu_seqlens, slot_of_seq, start_pos, state, slot_stride, copy_stride,
+                                              hist_off);
+    int rc = blm_check_launch("causal_conv");
+    if (rc != BLM_OK || K == 1) return rc;
+    dim3 grid2((channels + threads - 1) / threads, n_seqs);
+    conv_carry_kernel<<<grid2, threads, 0, stream>>>(x, x_stride, x_col0, channels, K, cu_seqlens, slot_of_seq, start_pos, state,
+                                                     slot_stride, copy_stride, hist_off);
+    return blm_check_launch("causal_conv (carry)");
+}
+
+// ---------------------------------------------------------------------------------------------
+// the scans
+// ---------------------------------------------------------------------------------------------
+struct ScanSeq {
+    int first, n_new, start;
+    const float* read;     // nullptr: the state is zero
+    float* write;
+};
+
+__device__ __forceinline__ ScanSeq scan_seq(int seq, const int* cu_seqlens, const int* slot_of_seq, const int* start_pos,
+                                            float* state, long long slot_stride, long long copy_stride, long long off) {
+    ScanSeq s;
+    s.first = cu_seqlens[seq];
+    s.n_new = cu_seqlens[seq + 1] - s.first;
+    s.start = start_pos[seq];
+    float* base = state + (size_t)slot_of_seq[seq < 0 ? 0 : seq] * slot_stride + off;
+    s.read = s.start > 0 ? base + (size_t)(s.start & 1) * copy_stride : nullptr;
+    s.write = base + (size_t)((s.start + s.n_new) & 1) * copy_stride;
+    return s;
+}
+
+__device__ __forceinline__ float group_sum(float v) {       // over the eight row groups of a column (adjacent lanes)
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    return v;
+}
+
+// State-space scan.  Per head h (group g = h / (heads / groups)), S [N x dv]:
+//     S <- exp(-exp(A_log_h) dt) S + dt B x^T;   y = S^T C + D_h x,    dt = softplus(dt_raw + dt_bias_h)
+// xbc [T, *]: x at x_col0 + h dv, B at b_col0 + g N, C at c_col0 + g N;  dt_raw [T, *] at dt_col0 + h.
+template <int RN>
+__global__ void __launch_bounds__(kCols* kRowGroups)
+    ssm_scan_kernel(const float* __restrict__ xbc, long long xbc_stride, int x_col0, int b_col0, int c_col0,
+                    const float* __restrict__ dt_raw, long long dt_stride, int dt_col0, const float* __restrict__ dt_bias,
+                    const float* __restrict__ A_log, const float* __restrict__ D, float* __restrict__ y, long long y_stride,
+                    int heads, int groups, int N, int dv, const int* __restrict__ cu_seqlens, const int* __restrict__ slot_of_seq,
+                    const int* __restrict__ start_pos, float* __restrict__ state, long long slot_stride, long long copy_stride,
+                    long long state_off) {
+    constexpr int NP = RN * kRowGroups;
+    extern __shared__ float sm[];
+    float* Bs = sm;                         // [kChunk][NP]
+    float* Cs = Bs + kChunk * NP;           // [kChunk][NP]
+    float* xs = Cs + kChunk * NP;           // [kChunk][kCols]
+    float* dts = xs + kChunk * kCols;       // [kChunk]
+    float* decs = dts + kChunk;             // [kChunk]
+    const int seq = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * kCols;
+    const ScanSeq sq = scan_seq(seq, cu_seqlens, slot_of_seq, start_pos, state, slot_stride, copy_stride, state_off);
+    if (sq.n_new <= 0) return;
+    const int tid = threadIdx.x, col = tid / kRowGroups, rg = tid % kRowGroups;
+    const int g = h / (heads / groups);
+    const bool live = col0 + col < dv;
+    const size_t head_off = (size_t)h * RN * dv * kRowGroups;
+    float s[RN];
+#pragma unroll
+    for (int r = 0; r < RN; ++r)
+        s[r] = (sq.read && live) ? sq.read[head_off + ((size_t)r * dv + col0 + col) * kRowGroups + rg] : 0.f;
+    const float a = -expf(A_log[h]);
+    const float bias = dt_bias[h], skip = D[h];
+    for (int c0 = 0; c0 < sq.n_new; c0 += kChunk) {
+        const int nt = min(kChunk, sq.n_new - c0);
+        __syncthreads();
+        for (int e = tid; e < nt * NP; e += blockDim.x) {
+            const int t = e / NP, n = e % NP;
+            const float* row = xbc + (size_t)(sq.first + c0 + t) * xbc_stride;
+            Bs[e] = n < N ? row[b_col0 + g * N + n] : 0.f;
+            Cs[e] = n < N ? row[c_col0 + g * N + n] : 0.f;
+        }
+        for (int e = tid; e < nt * kCols; e += blockDim.x) {
+            const int t = e / kCols, p = e % kCols;
+            xs[e] = col0 + p < dv ? xbc[(size_t)(sq.first + c0 + t) * xbc_stride + x_col0 + h * dv + col0 + p] : 0.f;
+        }
+        for (int t = tid; t < nt; t += blockDim.x) {
+            const float dt = softplus_r(dt_raw[(size_t)(sq.first + c0 + t) * dt_stride + dt_col0 + h] + bias);
+            dts[t] = dt;
+            decs[t] = expf(a * dt);
+        }
+        __syncthreads();
+        for (int t = 0; t < nt; ++t) {
+            const float dec = decs[t], dt = dts[t], xv = xs[t * kCols + col];
+            const float* b = Bs + t * NP + rg;
+            const float* c = Cs + t * NP + rg;
+            float acc = 0.f;
+#pragma unroll
+            for (int r = 0; r < RN; ++r) {
+                s[r] = dec * s[r] + (dt * b[r * kRowGroups]) * xv;
+                acc += s[r] * c[r * kRowGroups];
+            }
+            acc = group_sum(acc);
+            if (rg == 0 && live) y[(size_t)(sq.first + c0 + t) * y_stride + h * dv + col0 + col] = acc + skip * xv;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int r = 0; r < RN; ++r) sq.write[head_off + ((size_t)r * dv + col0 + col) * kRowGroups + rg] = s[r];
+    }
+}
+
+// Gated delta rule.  Per head h (query/key head c = h / (heads / qk_heads)), S [dk x dv]:
+//     S <- g[:, None] S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+// with k, q made unit vectors (x / sqrt(sum x^2 + 1e-6)), q also times dk^(-1/2), beta = sigmoid(b_raw),
+// g = exp(-exp(A_log_h) softplus(a_raw + dt_bias)) per head and key channel.
+template <int RN>
+__global__ void __launch_bounds__(kCols* kRowGroups)
+    delta_scan_kernel(const float* __restrict__ q, long long q_stride, int q_col0, const float* __restrict__ k, long long k_stride,
+                      int k_col0, const float* __restrict__ v, long long v_stride, int v_col0, const float* __restrict__ b_raw,
+                      long long b_stride, int b_col0, const float* __restrict__ a_raw, long long a_stride, int a_col0,
+                      const float* __restrict__ dt_bias, const float* __restrict__ A_log, float* __restrict__ o, long long o_stride,
+                      int heads, int qk_heads, int dk, int dv, const int* __restrict__ cu_seqlens,
+                      const int* __restrict__ slot_of_seq, const int* __restrict__ start_pos, float* __restrict__ state,
+                      long long slot_stride, long long copy_stride, long long state_off) {
+    constexpr int NP = RN * kRowGroups;
+    extern __shared__ float sm[];
+    float* ks = sm;                          // [kChunk][NP]
+    float* qs = ks + kChunk * NP;            // [kChunk][NP]
+    float* gs = qs + kChunk * NP;            // [kChunk][NP]
+    float* vs = gs + kChunk * NP;            // [kChunk][kCols]
+    float* betas = vs + kChunk * kCols;      // [kChunk]
+    const int seq = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * kCols;
+    const ScanSeq sq = scan_seq(seq, cu_seqlens, slot_of_seq, start_pos, state, slot_stride, copy_stride, state_off);
+    if (sq.n_new <= 0) return;
+    const int tid = threadIdx.x, col = tid / kRowGroups, rg = tid % kRowGroups;
+    const int lane = tid & 31, warp = tid >> 5;
+    const int c = h / (heads / qk_heads);
+    const bool live = col0 + col < dv;
+    const size_t head_off = (size_t)h * RN * dv * kRowGroups;
+    float s[RN];
+#pragma unroll
+    for (int r = 0; r < RN; ++r)
+        s[r] = (sq.read && live) ? sq.read[head_off + ((size_t)r * dv + col0 + col) * kRowGroups + rg] : 0.f;
+    const float a = -expf(A_log[h]);
+    const float q_scale = 1.0f / sqrtf((float)dk);
+    for (int c0 = 0; c0 < sq.n_new; c0 += kChunk) {
+        const int nt = min(kChunk, sq.n_new - c0);
+        __syncthreads();
+        for (int e = tid; e < nt * NP; e += blockDim.x) {
+            const int t = e / NP, n = e % NP;
+            const size_t row = (size_t)(sq.first + c0 + t);
+            ks[e] = n < dk ? k[row * k_stride + k_col0 + c * dk + n] : 0.f;
+            qs[e] = n < dk ? q[row * q_stride + q_col0 + c * dk + n] : 0.f;
+            gs[e] = n < dk ? expf(a * softplus_r(a_raw[row * a_stride + a_col0 + h * dk + n] + dt_bias[h * dk + n])) : 1.f;
+        }
+        for (int e = tid; e < nt * kCols; e += blockDim.x) {
+            const int t = e / kCols, p = e % kCols;
+            vs[e] = col0 + p < dv ? v[(size_t)(sq.first + c0 + t) * v_stride + v_col0 + h * dv + col0 + p] : 0.f;
+        }
+        for (int t = tid; t < nt; t += blockDim.x)
+            betas[t] = sigmoid_f(b_raw[(size_t)(sq.first + c0 + t) * b_stride + b_col0 + h]);
+        __syncthreads();
+        for (int t = warp; t < nt; t += blockDim.x / 32) {       // unit vectors: a warp per token
+            float sk = 0.f, sqq = 0.f;
+            for (int n = lane; n < NP; n += 32) {
+                sk += ks[t * NP + n] * ks[t * NP + n];
+                sqq += qs[t * NP + n] * qs[t * NP + n];
+            }
+            sk = warp_sum(sk);
+            sqq = warp_sum(sqq);
+            const float ik = 1.0f / sqrtf(sk + 1e-6f), iq = q_scale / sqrtf(sqq + 1e-6f);
+            for (int n = lane; n < NP; n += 32) {
+                ks[t * NP + n] *= ik;
+                qs[t * NP + n] *= iq;
+            }
+        }
+        __syncthreads();
+        for (int t = 0; t < nt; ++t) {
+            const float beta = betas[t], vv = vs[t * kCols + col];
+            const float* kk = ks + t * NP + rg;
+            const float* qq = qs + t * NP + rg;
+            const float* gg = gs + t * NP + rg;
+            float acc = 0.f;
+#pragma unroll
+            for (int r = 0; r < RN; ++r) {
+                s[r] *= gg[r * kRowGroups];
+                acc += s[r] * kk[r * kRowGroups];
+            }
+            acc = group_sum(acc);
+            const float u = beta * (vv - acc);
+            float out = 0.f;
+#pragma unroll
+            for (int r = 0; r < RN; ++r) {
+                s[r] += kk[r * kRowGroups] * u;
+                out += s[r] * qq[r * kRowGroups];
+            }
+            out = group_sum(out);
+            if (rg == 0 && live) o[(size_t)(sq.first + c0 + t) * o_stride + h * dv + col0 + col] = out;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int r = 0; r < RN; ++r) sq.write[head_off + ((size_t)r * dv + col0 + col) * kRowGroups + rg] = s[r];
+    }
+}
+
+static int rows_per_thread(int n) {       // the smallest instance that holds n rows: 8 row groups x RN
+    for (int rn : {1, 2, 4, 8, 16, 32})
+        if (rn * kRowGroups >= n) return rn;
+    return 0;
+}
+
+// floats of one copy of a scan's state: heads x (rows rounded up to its instance) x dv
+BLM_API long long blm_scan_state_floats(int heads, int rows, int dv) {
+    const int rn = rows_per_thread(rows);
+    return rn ? (long long)heads * rn * kRowGroups * dv : -1;
+}
+
+template <typename Kern>
+static int allow_smem(Kern k, size_t smem, const char* what) {
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "%s: %s", what, cudaGetErrorString(e));
+    }
+    return BLM_OK;
+}
+
+BLM_API int blm_ssm_scan(const float* xbc, long long xbc_stride, int x_col0, int b_col0, int c_col0, const float* dt_raw,
+                         long long dt_stride, int dt_col0, const float* dt_bias, const float* A_log, const float* D, float* y,
+                         long long y_stride, int heads, int groups, int N, int dv, const int* cu_seqlens, const int* slot_of_seq,
+                         const int* start_pos, int n_seqs, float* state, long long slot_stride, long long copy_stride,
+                         long long state_off, cudaStream_t stream) {
+    if (n_seqs == 0) return BLM_OK;
+    const int rn = rows_per_thread(N);
+    BLM_REQUIRE(rn > 0, "ssm_scan: a state of %d rows; this kernel takes up to %d", N, 32 * kRowGroups);
+    BLM_REQUIRE(heads > 0 && groups > 0 && heads % groups == 0 && dv > 0, "ssm_scan: bad head counts");
+    BLM_REQUIRE(heads <= 65535 && (dv + kCols - 1) / kCols <= 65535, "ssm_scan: too many heads");
+    dim3 grid(n_seqs, heads, (dv + kCols - 1) / kCols);
+    const size_t smem = ((size_t)2 * kChunk * rn * kRowGroups + kChunk * kCols + 2 * kChunk) * sizeof(float);
+#define BLM_SSM(RN)                                                                                                          \
+    case RN: {                                                                                                               \
+        int rc = allow_smem(ssm_scan_kernel<RN>, smem, "ssm_scan");                                                          \
+        if (rc != BLM_OK) return rc;                                                                                         \
+        ssm_scan_kernel<RN><<<grid, kCols * kRowGroups, smem, stream>>>(xbc, xbc_stride, x_col0, b_col0, c_col0, dt_raw,     \
+            dt_stride, dt_col0, dt_bias, A_log, D, y, y_stride, heads, groups, N, dv, cu_seqlens, slot_of_seq, start_pos,    \
+            state, slot_stride, copy_stride, state_off);                                                                     \
+        break;                                                                                                               \
+    }
+    switch (rn) {
+        BLM_SSM(1) BLM_SSM(2) BLM_SSM(4) BLM_SSM(8) BLM_SSM(16) BLM_SSM(32)
+    }
+#undef BLM_SSM
+    return blm_check_launch("ssm_scan");
+}
+
+BLM_API int blm_delta_scan(const float* q, long long q_stride, int q_col0, const float* k, long long k_stride, int k_col0,
+                           const float* v, long long v_stride, int v_col0, const float* b_raw, long long b_stride, int b_col0,
+                           const float* a_raw, long long a_stride, int a_col0, const float* dt_bias, const float* A_log, float* o,
+                           long long o_stride, int heads, int qk_heads, int dk, int dv, const int* cu_seqlens,
+                           const int* slot_of_seq, const int* start_pos, int n_seqs, float* state, long long slot_stride,
+                           long long copy_stride, long long state_off, cudaStream_t stream) {
+    if (n_seqs == 0) return BLM_OK;
+    const int rn = rows_per_thread(dk);
+    BLM_REQUIRE(rn > 0, "delta_scan: keys of %d lanes; this kernel takes up to %d", dk, 32 * kRowGroups);
+    BLM_REQUIRE(heads > 0 && qk_heads > 0 && heads % qk_heads == 0 && dv > 0, "delta_scan: bad head counts");
+    BLM_REQUIRE(heads <= 65535 && (dv + kCols - 1) / kCols <= 65535, "delta_scan: too many heads");
+    dim3 grid(n_seqs, heads, (dv + kCols - 1) / kCols);
+    const size_t smem = ((size_t)3 * kChunk * rn * kRowGroups + kChunk * kCols + kChunk) * sizeof(float);
+#define BLM_DELTA(RN)                                                                                                        \
+    case RN: {                                                                                                               \
+        int rc = allow_smem(delta_scan_kernel<RN>, smem, "delta_scan");                                                      \
+        if (rc != BLM_OK) return rc;                                                                                         \
+        delta_scan_kernel<RN><<<grid, kCols * kRowGroups, smem, stream>>>(q, q_stride, q_col0, k, k_stride, k_col0, v,       \
+            v_stride, v_col0, b_raw, b_stride, b_col0, a_raw, a_stride, a_col0, dt_bias, A_log, o, o_stride, heads,          \
+            qk_heads, dk, dv, cu_seqlens, slot_of_seq, start_pos, state, slot_stride, copy_stride, state_off);               \
+        break;                                                                                                               \
+    }
+    switch (rn) {
+        BLM_DELTA(1) BLM_DELTA(2) BLM_DELTA(4) BLM_DELTA(8) BLM_DELTA(16) BLM_DELTA(32)
+    }
+#undef BLM_DELTA
+    return blm_check_launch("delta_scan");
+}
+
+// ---------------------------------------------------------------------------------------------
+// RMS norm over groups of a row's lanes, with a gate
+//   mode 0 (gate first):  u = y silu(gate);  out = u / sqrt(mean_group(u^2) + eps) * w[lane % period]
+//   mode 1 (gate last):   out = y / sqrt(mean_group(y^2) + eps) * w[lane % period] * sigmoid(gate)
+// A warp per (row, group).  Rows of no sequence hold zeros and give zeros.
+// ---------------------------------------------------------------------------------------------
+template <typename TA>
+__global__ void gated_group_norm_kernel(const float* __restrict__ y, long long y_stride, const float* __restrict__ gate,
+                                        long long gate_stride, int gate_col0, const float* __restrict__ w, int period,
+                                        int group, int n_groups, int mode, float eps, TA* __restrict__ out, long long out_stride) {
+    const int n = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const float* yr = y + (size_t)n * y_stride;
+    const float* gr = gate + (size_t)n * gate_stride + gate_col0;
+    TA* orow = out + (size_t)n * out_stride;
+    for (int g = warp; g < n_groups; g += n_warps) {
+        const int lo = g * group;
+        float ss = 0.f;
+        for (int i = lane; i < group; i += 32) {
+            float u = yr[lo + i];
+            if (mode == 0) u *= silu_f(gr[lo + i]);
+            ss += u * u;
+        }
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss / (float)group + eps);
+        for (int i = lane; i < group; i += 32) {
+            float u = yr[lo + i];
+            const float gv = gr[lo + i];
+            if (mode == 0) u = u * silu_f(gv) * inv * w[(lo + i) % period];
+            else u = u * inv * w[(lo + i) % period] * sigmoid_f(gv);
+            orow[lo + i] = from_f32<TA>(u);
+        }
+    }
+}
+
+BLM_API int blm_gated_group_norm(const float* y, long long y_stride, const float* gate, long long gate_stride, int gate_col0,
+                                 const float* w, int period, int group, int n_groups, int mode, float eps, void* out,
+                                 int out_dtype, long long out_stride, int n, cudaStream_t stream) {
+    if (n == 0) return BLM_OK;
+    BLM_REQUIRE(group > 0 && n_groups > 0 && period > 0 && (mode == 0 || mode == 1), "gated_group_norm: bad sizes or mode");
+    const int threads = n_groups >= 8 ? 256 : 32 * n_groups;
+    if (out_dtype == BLM_F32)
+        gated_group_norm_kernel<float><<<n, threads, 0, stream>>>(y, y_stride, gate, gate_stride, gate_col0, w, period, group,
+                                                                  n_groups, mode, eps, (float*)out, out_stride);
+    else if (out_dtype == BLM_BF16)
+        gated_group_norm_kernel<__nv_bfloat16><<<n, threads, 0, stream>>>(y, y_stride, gate, gate_stride, gate_col0, w, period,
+                                                                          group, n_groups, mode, eps, (__nv_bfloat16*)out, out_stride);
+    else
+        return blm_fail(BLM_BAD_ARGUMENT, "gated_group_norm: out dtype %d", out_dtype);
+    return blm_check_launch("gated_group_norm");
+}

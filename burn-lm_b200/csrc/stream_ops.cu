@@ -1,0 +1,167 @@
+// Row-wise kernels around the residual stream for blocks that norm a sublayer's output before it is added:
+// a scaled embedding gather, the add of a normed (and scaled) output fused with the norm that reads the stream
+// next, and a bias with an optional activation.  Statistics, sums and the activation are fp32.
+#include "common.cuh"
+
+BLM_API const char* blm_stream_ops_last_error() { return g_blm_error; }
+
+// ---------------------------------------------------------------------------------------------
+// out[n, :] = table[tokens[n], :] * scale  (fp32 stream from a bf16 or fp32 table)
+// ---------------------------------------------------------------------------------------------
+template <typename TT>
+__global__ void embed_scaled_kernel(const int* __restrict__ tokens, const TT* __restrict__ table, float* __restrict__ out,
+                                    int width, int vocab, float scale) {
+    const int n = blockIdx.x;
+    int tok = tokens[n];
+    if ((unsigned)tok >= (unsigned)vocab) tok = 0;  // ids are validated on the host; never read wild
+    const TT* row = table + (size_t)tok * width;
+    float* o = out + (size_t)n * width;
+    for (int d = threadIdx.x; d < width; d += blockDim.x) o[d] = to_f32(row[d]) * scale;
+}
+
+BLM_API int blm_embed_scaled(const int* tokens, const void* table, int table_dtype, float* out, int n, int width, int vocab,
+                             float scale, cudaStream_t stream) {
+    if (n == 0) return BLM_OK;
+    BLM_REQUIRE(n > 0 && width > 0 && vocab > 0, "embed_scaled: bad sizes");
+    const int threads = width >= 1024 ? 256 : 128;
+    if (table_dtype == BLM_BF16)
+        embed_scaled_kernel<__nv_bfloat16><<<n, threads, 0, stream>>>(tokens, (const __nv_bfloat16*)table, out, width, vocab, scale);
+    else if (table_dtype == BLM_F32)
+        embed_scaled_kernel<float><<<n, threads, 0, stream>>>(tokens, (const float*)table, out, width, vocab, scale);
+    else
+        return blm_fail(BLM_BAD_ARGUMENT, "embed_scaled: table dtype %d", table_dtype);
+    return blm_check_launch("embed_scaled");
+}
+
+// ---------------------------------------------------------------------------------------------
+// The sandwich step.  With d = delta (+ bias), a sublayer's raw output:
+//     h   = resid + mult * (d / sqrt(mean(d^2) + eps_post) * post_w)          (stored unless `rows`)
+//     out = h / sqrt(mean(h^2) + eps_pre) * pre_w                             (when pre_w is given)
+// delta null: h = resid.  rows given: row b of `out` comes from row rows[b]; the stream is left alone.
+// ---------------------------------------------------------------------------------------------
+template <typename TD, typename TA>
+__global__ void sandwich_norm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, const float* __restrict__ bias,
+                                     const float* __restrict__ post_w, const float* __restrict__ pre_w, float mult,
+                                     float eps_post, float eps_pre, TA* __restrict__ out, const int* __restrict__ rows,
+                                     int width) {
+    extern __shared__ float row_buf[];      // [width] + 33
+    float* red = row_buf + width;
+    const int src = rows ? rows[blockIdx.x] : blockIdx.x;
+    float* r = resid + (size_t)src * width;
+    float inv_d = 0.f;
+    if (delta) {
+        const TD* dl = delta + (size_t)src * width;
+        float ss = 0.f;
+        for (int d = threadIdx.x; d < width; d += blockDim.x) {
+            float v = to_f32(dl[d]);
+            if (bias) v += bias[d];
+            row_buf[d] = v;
+            ss += v * v;
+        }
+        const float total = block_sum(ss, red);
+        inv_d = 1.0f / sqrtf(total / (float)width + eps_post);
+    }
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < width; d += blockDim.x) {
+        float h = r[d];
+        if (delta) {
+            h += mult * (row_buf[d] * inv_d * post_w[d]);
+            if (!rows) r[d] = h;
+        }
+        row_buf[d] = h;
+        ss += h * h;
+    }
+    if (pre_w == nullptr || out == nullptr) return;
+    const float total = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(total / (float)width + eps_pre);
+    TA* o = out + (size_t)blockIdx.x * width;
+    for (int d = threadIdx.x; d < width; d += blockDim.x) o[d] = from_f32<TA>(row_buf[d] * inv * pre_w[d]);
+}
+
+template <typename TD, typename TA>
+static int launch_sandwich(float* resid, const void* delta, const float* bias, const float* post_w, const float* pre_w, float mult,
+                           float eps_post, float eps_pre, void* out, const int* rows, int n_rows, int width, cudaStream_t stream) {
+    const size_t smem = (size_t)(width + 33) * sizeof(float);
+    BLM_REQUIRE(smem <= 200 * 1024, "sandwich norm: width %d is beyond what this kernel holds in shared memory", width);
+    auto k = sandwich_norm_kernel<TD, TA>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "sandwich norm: %s", cudaGetErrorString(e));
+    }
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    k<<<n_rows, threads, smem, stream>>>(resid, (const TD*)delta, bias, post_w, pre_w, mult, eps_post, eps_pre, (TA*)out, rows, width);
+    return blm_check_launch("sandwich_norm");
+}
+
+BLM_API int blm_sandwich_norm(float* resid, const void* delta, int delta_dtype, const float* bias, const float* post_w,
+                              const float* pre_w, float mult, float eps_post, float eps_pre, void* out, int out_dtype,
+                              const int* rows, int n_rows, int width, cudaStream_t stream) {
+    if (n_rows == 0) return BLM_OK;
+    BLM_REQUIRE(n_rows > 0 && width > 0, "sandwich norm: bad sizes");
+    BLM_REQUIRE(delta == nullptr || post_w != nullptr, "sandwich norm: an output to add needs its norm's weight");
+#define BLM_SW(TD, TA) return launch_sandwich<TD, TA>(resid, delta, bias, post_w, pre_w, mult, eps_post, eps_pre, out, rows, n_rows, width, stream)
+    if (delta_dtype == BLM_F32 && out_dtype == BLM_F32) BLM_SW(float, float);
+    if (delta_dtype == BLM_F32 && out_dtype == BLM_BF16) BLM_SW(float, __nv_bfloat16);
+    if (delta_dtype == BLM_BF16 && out_dtype == BLM_F32) BLM_SW(__nv_bfloat16, float);
+    if (delta_dtype == BLM_BF16 && out_dtype == BLM_BF16) BLM_SW(__nv_bfloat16, __nv_bfloat16);
+#undef BLM_SW
+    return blm_fail(BLM_BAD_ARGUMENT, "sandwich norm: dtypes %d/%d", delta_dtype, out_dtype);
+}
+
+// ---------------------------------------------------------------------------------------------
+// out = act(x + bias).  kind 0: identity.  kind 1: xIELU with the two numbers params = (p, q):
+//     z > 0:  softplus(p) z^2 + z / 2;     z <= 0:  (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float softplus_f(float v) { return fmaxf(v, 0.f) + log1pf(expf(-fabsf(v))); }
+
+template <typename TI, typename TA>
+__global__ void bias_act_kernel(const TI* __restrict__ x, const float* __restrict__ bias, const float* __restrict__ params,
+                                TA* __restrict__ out, size_t total, int width, int kind) {
+    float ap = 0.f, an = 0.f;
+    if (kind == 1) {
+        ap = softplus_f(params[0]);
+        an = 0.5f + softplus_f(params[1]);
+    }
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        float z = to_f32(x[i]);
+        if (bias) z += bias[i % width];
+        if (kind == 1) z = z > 0.f ? ap * z * z + 0.5f * z : an * (expm1f(z) - z) + 0.5f * z;
+        out[i] = from_f32<TA>(z);
+    }
+}
+
+BLM_API int blm_bias_act(const void* x, int x_dtype, const float* bias, const float* params, void* out, int out_dtype, int n,
+                         int width, int kind, cudaStream_t stream) {
+    if (n == 0) return BLM_OK;
+    BLM_REQUIRE(n > 0 && width > 0 && (kind == 0 || kind == 1), "bias_act: bad sizes or kind");
+    BLM_REQUIRE(kind == 0 || params != nullptr, "bias_act: the activation needs its two numbers");
+    const size_t total = (size_t)n * width;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 65535u * 16u ? (total + threads - 1) / threads : 65535u * 16u);
+#define BLM_BA(TI, TA) bias_act_kernel<TI, TA><<<blocks, threads, 0, stream>>>((const TI*)x, bias, params, (TA*)out, total, width, kind)
+    if (x_dtype == BLM_F32 && out_dtype == BLM_F32) BLM_BA(float, float);
+    else if (x_dtype == BLM_F32 && out_dtype == BLM_BF16) BLM_BA(float, __nv_bfloat16);
+    else if (x_dtype == BLM_BF16 && out_dtype == BLM_BF16) BLM_BA(__nv_bfloat16, __nv_bfloat16);
+    else if (x_dtype == BLM_BF16 && out_dtype == BLM_F32) BLM_BA(__nv_bfloat16, float);
+    else return blm_fail(BLM_BAD_ARGUMENT, "bias_act: dtypes %d/%d", x_dtype, out_dtype);
+#undef BLM_BA
+    return blm_check_launch("bias_act");
+}
+
+// ---------------------------------------------------------------------------------------------
+// out = sa a + sb b  (fp32): the sum of two mixers that ran side by side
+// ---------------------------------------------------------------------------------------------
+__global__ void weighted_sum_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out, float sa,
+                                    float sb, size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = sa * a[i] + sb * b[i];
+}
+
+BLM_API int blm_weighted_sum(const float* a, const float* b, float* out, float sa, float sb, size_t total, cudaStream_t stream) {
+    if (total == 0) return BLM_OK;
+    const int threads = 256;
+    const size_t want = (total + threads - 1) / threads;
+    const int blocks = (int)(want < 65535u * 16u ? want : 65535u * 16u);
+    weighted_sum_kernel<<<blocks, threads, 0, stream>>>(a, b, out, sa, sb, total);
+    return blm_check_launch("weighted_sum");
+}

@@ -97,6 +97,35 @@ _protos = {
         "blm_attention_sink_prompt_takes": [c_int, c_int, c_int, c_int, c_int, c_int],
         "blm_attention_sink_decode_takes": [c_int, c_int, c_int, c_int, c_int, c_int],
     },
+    "stream_ops": {
+        "blm_embed_scaled": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+        "blm_sandwich_norm": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_float, c_float, c_void_p, c_int,
+                              c_void_p, c_int, c_int, c_void_p],
+        "blm_bias_act": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "blm_weighted_sum": [c_void_p, c_void_p, c_void_p, c_float, c_float, c_size_t, c_void_p],
+    },
+    "recurrent": {
+        "blm_causal_conv": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_longlong, c_int,
+                            c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_longlong, c_longlong, c_longlong,
+                            c_void_p],
+        "blm_ssm_scan": [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p,
+                         c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                         c_longlong, c_longlong, c_longlong, c_void_p],
+        "blm_delta_scan": [c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_int, c_void_p,
+                           c_longlong, c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int,
+                           c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_longlong, c_longlong,
+                           c_void_p],
+        "blm_gated_group_norm": [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                                 c_float, c_void_p, c_int, c_longlong, c_int, c_void_p],
+    },
+    "attention_sigmoid": {
+        "blm_bias_rope_append": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "blm_sigmoid_attention": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                  c_float, c_float, c_void_p],
+        "blm_sigmoid_attention_takes": [c_int, c_int, c_int, c_int, c_int, c_int],
+    },
     "moe": {
         "blm_moe_route": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
         "blm_moe_group": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -903,3 +932,222 @@ def uniform32(seed, stream_id, counter) -> int:
     fn.argtypes = [c_ulonglong, c_ulonglong, c_ulonglong]
     fn.restype = c_uint
     return int(fn(seed & (2**64 - 1), stream_id & (2**64 - 1), counter & (2**64 - 1)))
+
+
+# ------------------------------------------------------------------------------------------------
+# blocks that norm a sublayer's output before it is added to the stream
+# ------------------------------------------------------------------------------------------------
+def _f32(*tensors):
+    for t in tensors:
+        if t is not None and t.dtype != torch.float32:
+            raise KernelError("this argument must be float32")
+
+
+def embed_scaled(tokens, table, out, scale: float):
+    """out[n, :] = table[tokens[n], :] * scale as fp32.  tokens int32 [N]; table [V, D]; out fp32 [N, D]."""
+    _need_cuda(tokens, table, out)
+    n, (v, d) = tokens.numel(), table.shape
+    if tokens.dtype != torch.int32 or out.dtype != torch.float32 or tuple(out.shape) != (n, d):
+        raise KernelError("embed_scaled: tokens int32 [N], out float32 [N, D]")
+    _call("stream_ops", "blm_embed_scaled", _ptr(tokens), _ptr(table), _code(table.dtype), _ptr(out), n, d, v, c_float(scale), _stream())
+
+
+def sandwich_norm(resid, delta, post_weight, mult, eps_post, pre_weight, eps_pre, out, rows=None, delta_bias=None):
+    """The add of a normed sublayer output fused with the norm that reads the stream next, in fp32.  With d = delta (+ delta_bias):
+
+        h   = resid + mult * (d / sqrt(mean(d^2) + eps_post) * post_weight)       stored into resid (rows is None)
+        out = h / sqrt(mean(h^2) + eps_pre) * pre_weight                          when pre_weight and out are given
+
+    delta None: h = resid.  rows (int32 [R]): row i of out comes from row rows[i], resid is left alone.
+    resid fp32 [N, D]; delta [N, D] in float32 or bfloat16; the weights and the bias float32 [D]."""
+    _need_cuda(resid, delta, post_weight, pre_weight, out, rows, delta_bias)
+    _f32(resid, post_weight, pre_weight, delta_bias)
+    d = resid.shape[-1]
+    n_out = rows.numel() if rows is not None else resid.shape[0]
+    if delta is not None and (delta.shape != resid.shape or post_weight is None or post_weight.numel() != d):
+        raise KernelError("sandwich_norm: delta must match resid's shape and bring its norm's weight [D]")
+    if out is not None and (tuple(out.shape) != (n_out, d) or pre_weight is None or pre_weight.numel() != d):
+        raise KernelError("sandwich_norm: out [rows, D] needs the weight [D] of the norm that produces it")
+    if rows is not None and rows.dtype != torch.int32:
+        raise KernelError("sandwich_norm: rows must be int32")
+    _call("stream_ops", "blm_sandwich_norm", _ptr(resid), _ptr(delta), _code(delta.dtype) if delta is not None else F32,
+          _ptr(delta_bias), _ptr(post_weight), _ptr(pre_weight if out is not None else None), c_float(mult), c_float(eps_post),
+          c_float(eps_pre), _ptr(out), _code(out.dtype) if out is not None else F32, _ptr(rows), n_out, d, _stream())
+
+
+ACT_NONE, ACT_XIELU = 0, 1
+
+
+def bias_act(x, bias, out, kind=ACT_NONE, params=None):
+    """out = act(x + bias) row by row; x, out [N, D] (float32 or bfloat16), bias float32 [D] or None.  ACT_XIELU with
+    params = float32 [2] (p, q): z > 0: softplus(p) z^2 + z / 2; else (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2."""
+    _need_cuda(x, bias, out, params)
+    _f32(bias, params)
+    n, d = x.shape
+    if tuple(out.shape) != (n, d) or (bias is not None and bias.numel() != d):
+        raise KernelError("bias_act: x and out [N, D], bias [D]")
+    if kind == ACT_XIELU and (params is None or params.numel() != 2):
+        raise KernelError("bias_act: the activation needs its two numbers")
+    _call("stream_ops", "blm_bias_act", _ptr(x), _code(x.dtype), _ptr(bias), _ptr(params), _ptr(out), _code(out.dtype), n, d, int(kind),
+          _stream())
+
+
+def weighted_sum(a, scale_a, b, scale_b, out):
+    """out = scale_a * a + scale_b * b, all float32 of one shape."""
+    _need_cuda(a, b, out)
+    _f32(a, b, out)
+    if a.shape != b.shape or a.shape != out.shape:
+        raise KernelError("weighted_sum: shapes differ")
+    _call("stream_ops", "blm_weighted_sum", _ptr(a), _ptr(b), _ptr(out), c_float(scale_a), c_float(scale_b), c_size_t(a.numel()), _stream())
+
+
+# ------------------------------------------------------------------------------------------------
+# recurrent mixers
+# ------------------------------------------------------------------------------------------------
+SCAN_ROW_GROUPS = 8
+
+
+def scan_state_floats(heads: int, rows: int, value_dim: int) -> int:
+    """Floats of one copy of a scan's state: the rows are rounded up to what the kernel's instance holds."""
+    for rn in (1, 2, 4, 8, 16, 32):
+        if rn * SCAN_ROW_GROUPS >= rows:
+            return heads * rn * SCAN_ROW_GROUPS * value_dim
+    raise KernelError(f"a recurrent state of {rows} rows: the scan kernels take up to {32 * SCAN_ROW_GROUPS}")
+
+
+def _state_args(state, offset):
+    """state float32 [slots, 2, floats]: (pointer, floats a slot, floats a copy, this piece's offset in a copy)."""
+    if state.dtype != torch.float32 or state.dim() != 3 or state.shape[1] != 2 or not state.is_contiguous():
+        raise KernelError("a recurrent state is float32 [slots, 2, floats]")
+    return _ptr(state), c_longlong(2 * state.shape[2]), c_longlong(state.shape[2]), c_longlong(offset)
+
+
+def _cols(t, col0, width):
+    if t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1 or col0 < 0 or col0 + width > t.shape[1]:
+        raise KernelError("a column range must lie inside a float32 [N, *] tensor with unit stride along its rows")
+    return _ptr(t), c_longlong(t.stride(0)), int(col0)
+
+
+def causal_conv(x, x_col0, channels, taps, bias, out, out_col0, step, state, state_offset, silu=True):
+    """y_t = sum_k taps[:, k] x_(t - (K-1) + k) (+ bias) per channel over each sequence's time, then silu; zeros before a
+    sequence's start.  x, out float32 [N, *] (the channels at x_col0 / out_col0); taps float32 [C, K]; the last K - 1
+    inputs of every sequence are carried in `state` (float32 [slots, 2, floats]) at state_offset, [K - 1, C]."""
+    _need_cuda(taps, bias, state)
+    _f32(taps, bias)
+    k = taps.shape[1]
+    if tuple(taps.shape) != (channels, k) or (bias is not None and bias.numel() != channels):
+        raise KernelError("causal_conv: taps [C, K], bias [C]")
+    xp, xs, xc = _cols(x, x_col0, channels)
+    op, os_, oc = _cols(out, out_col0, channels)
+    if x.shape[0] != step.n_tokens or out.shape[0] != step.n_tokens:
+        raise KernelError("causal_conv: a row per token of the step")
+    _call("recurrent", "blm_causal_conv", xp, xs, xc, channels, _ptr(taps), _ptr(bias), k, 1 if silu else 0, op, os_, oc,
+          _ptr(step.token_seq), _ptr(step.cu_seqlens), _ptr(step.slot_of_seq), _ptr(step.start_pos), step.n_tokens, step.n_seqs,
+          *_state_args(state, state_offset), _stream(), kernels=2 if k > 1 else 1)
+
+
+def ssm_scan(xbc, x_col0, b_col0, c_col0, dt, dt_col0, dt_bias, a_log, d_skip, y, heads, groups, n_state, value_dim, step, state,
+             state_offset):
+    """The state-space scan per head: S <- exp(-exp(A_log) dt) S + dt B x^T, y = S^T C + D x with dt = softplus(dt_raw +
+    dt_bias); x [heads x value_dim], B and C [groups x n_state] are column ranges of xbc, dt_raw [heads] one of dt;
+    y float32 [N, heads * value_dim].  The state (fp32, carried per sequence) lies in `state` at state_offset."""
+    _need_cuda(dt_bias, a_log, d_skip, y, state)
+    _f32(dt_bias, a_log, d_skip, y)
+    xp, xs, xc = _cols(xbc, x_col0, heads * value_dim)
+    _cols(xbc, b_col0, groups * n_state)
+    _cols(xbc, c_col0, groups * n_state)
+    dp, ds, dc = _cols(dt, dt_col0, heads)
+    if tuple(y.shape) != (step.n_tokens, heads * value_dim) or not y.is_contiguous():
+        raise KernelError("ssm_scan: y float32 [N, heads * value_dim]")
+    _call("recurrent", "blm_ssm_scan", xp, xs, xc, int(b_col0), int(c_col0), dp, ds, dc, _ptr(dt_bias), _ptr(a_log), _ptr(d_skip),
+          _ptr(y), c_longlong(y.stride(0)), heads, groups, n_state, value_dim, _ptr(step.cu_seqlens), _ptr(step.slot_of_seq),
+          _ptr(step.start_pos), step.n_seqs, *_state_args(state, state_offset), _stream())
+
+
+def delta_scan(q, q_col0, k, k_col0, v, v_col0, b, b_col0, a, a_col0, dt_bias, a_log, out, heads, qk_heads, key_dim, value_dim,
+               step, state, state_offset):
+    """The gated delta rule per head: S <- g S (g per key channel); u = beta (v - S^T k); S <- S + k u^T; o = S^T q, with
+    q and k made unit vectors (q also times key_dim^-1/2), beta = sigmoid(b), g = exp(-exp(A_log) softplus(a + dt_bias)).
+    q, k [qk_heads x key_dim], v [heads x value_dim], b [heads], a [heads x key_dim] are column ranges of float32 [N, *]
+    tensors; out float32 [N, heads * value_dim]."""
+    _need_cuda(dt_bias, a_log, out, state)
+    _f32(dt_bias, a_log, out)
+    qa = _cols(q, q_col0, qk_heads * key_dim)
+    ka = _cols(k, k_col0, qk_heads * key_dim)
+    va = _cols(v, v_col0, heads * value_dim)
+    ba = _cols(b, b_col0, heads)
+    aa = _cols(a, a_col0, heads * key_dim)
+    if tuple(out.shape) != (step.n_tokens, heads * value_dim) or not out.is_contiguous() or dt_bias.numel() != heads * key_dim:
+        raise KernelError("delta_scan: out float32 [N, heads * value_dim], dt_bias [heads * key_dim]")
+    _call("recurrent", "blm_delta_scan", *qa, *ka, *va, *ba, *aa, _ptr(dt_bias), _ptr(a_log), _ptr(out), c_longlong(out.stride(0)),
+          heads, qk_heads, key_dim, value_dim, _ptr(step.cu_seqlens), _ptr(step.slot_of_seq), _ptr(step.start_pos), step.n_seqs,
+          *_state_args(state, state_offset), _stream())
+
+
+GATE_FIRST, GATE_LAST = 0, 1
+
+
+def gated_group_norm(y, gate, gate_col0, weight, group, mode, eps, out):
+    """RMS norm over groups of `group` lanes of every row with a gate.  GATE_FIRST: u = y silu(gate), out = u / rms(u) *
+    weight; GATE_LAST: out = y / rms(y) * weight * sigmoid(gate).  weight float32 of a row's or of a group's size (then
+    shared by the groups); y float32 [N, C]; the gate a column range of a float32 tensor; out [N, C]."""
+    _need_cuda(y, weight, out)
+    _f32(y, weight)
+    n, c = y.shape
+    if c % group or weight.numel() not in (c, group) or tuple(out.shape) != (n, c) or not y.is_contiguous() or not out.is_contiguous():
+        raise KernelError("gated_group_norm: groups must divide the row; weight of a row's or a group's size")
+    gp, gs, gc = _cols(gate, gate_col0, c)
+    _call("recurrent", "blm_gated_group_norm", _ptr(y), c_longlong(y.stride(0)), gp, gs, gc, _ptr(weight), weight.numel(), group,
+          c // group, int(mode), c_float(eps), _ptr(out), _code(out.dtype), c_longlong(out.stride(0)), n, _stream())
+
+
+# ------------------------------------------------------------------------------------------------
+# attention without a softmax
+# ------------------------------------------------------------------------------------------------
+def bias_rope_append(proj, bias, freq, rotary_dim, q_out, pool, block_table, step, n_heads, n_kv, key_dim, value_dim):
+    """proj float32 [N, q | k | v] (+ bias float32): the first rotary_dim lanes of every q and k head are rotated (lane i
+    with lane i + rotary_dim / 2 by position * freq[i], freq float32 [rotary_dim / 2], the angle in fp32); q goes to q_out
+    [N, n_heads * key_dim], k and v to the token's place in the paged cache."""
+    _need_cuda(proj, bias, freq, q_out, pool, block_table)
+    _f32(proj, bias, freq)
+    n = step.n_tokens
+    width = (n_heads + n_kv) * key_dim + n_kv * value_dim
+    if proj.dim() != 2 or proj.shape[0] != n or proj.shape[1] != width or (bias is not None and bias.numel() != width):
+        raise KernelError("bias_rope_append: proj [N, (heads + kv) * key_dim + kv * value_dim] and a bias of that width")
+    if q_out.dtype != pool.dtype or tuple(q_out.shape) != (n, n_heads * key_dim):
+        raise KernelError("bias_rope_append: q_out [N, heads * key_dim] in the cache's dtype")
+    if pool.numel() % kv_page_elems(n_kv, key_dim, value_dim):
+        raise KernelError("bias_rope_append: the pool does not consist of pages of keys [kv, PAGE, key_dim] and values [kv, PAGE, value_dim]")
+    if rotary_dim and (freq is None or freq.numel() != rotary_dim // 2):
+        raise KernelError("bias_rope_append: freq must be float32 [rotary_dim / 2]")
+    _call("attention_sigmoid", "blm_bias_rope_append", _ptr(proj), c_longlong(proj.stride(0)), _ptr(bias), _ptr(freq), int(rotary_dim),
+          _ptr(q_out), _ptr(pool), _code(pool.dtype), _ptr(step.token_seq), _ptr(step.token_pos), _ptr(step.slot_of_seq),
+          _ptr(block_table), block_table.shape[1], n, n_heads, n_kv, key_dim, value_dim, PAGE, _stream())
+
+
+def sigmoid_attention_takes(dtype, n_heads, n_kv, key_dim, value_dim) -> bool:
+    return bool(_lib("attention_sigmoid").blm_sigmoid_attention_takes(_code(dtype), n_heads, n_kv, key_dim, value_dim, PAGE))
+
+
+def sigmoid_attention(q, pool, block_table, step, out, n_heads, n_kv, key_dim, value_dim, scale, softcap=0.0, talk=None,
+                      head_bias=None, ranges=1, partial=None):
+    """Causal attention whose weights are sigmoid(cap(scale q.k) + head_bias) without a normalisation over the keys, mixed
+    across heads by talk [heads, heads] (row h: what head h takes of every head's weights) before they meet the values.
+    q [N, heads * key_dim] and out [N, heads * value_dim] in the cache's dtype (out must hold zeros in rows of no
+    sequence); `ranges` > 1 cuts every query's keys over that many blocks whose partial outputs (`partial`, float32
+    with room for ranges * N * heads * value_dim) are added in order."""
+    _need_cuda(q, pool, block_table, out, talk, head_bias, partial)
+    _f32(talk, head_bias, partial)
+    n = step.n_tokens
+    if q.dtype != pool.dtype or out.dtype != pool.dtype or tuple(q.shape) != (n, n_heads * key_dim) or tuple(out.shape) != (n, n_heads * value_dim):
+        raise KernelError("sigmoid_attention: q [N, heads * key_dim], out [N, heads * value_dim] in the cache's dtype")
+    if talk is not None and tuple(talk.shape) != (n_heads, n_heads):
+        raise KernelError("sigmoid_attention: talk [heads, heads]")
+    if head_bias is not None and head_bias.numel() != n_heads:
+        raise KernelError("sigmoid_attention: head_bias [heads]")
+    if ranges > 1 and (partial is None or partial.numel() < ranges * n * n_heads * value_dim):
+        raise KernelError("sigmoid_attention: the workspace is too small for the key ranges")
+    _call("attention_sigmoid", "blm_sigmoid_attention", _ptr(q), _ptr(pool), _code(pool.dtype), _ptr(block_table), block_table.shape[1],
+          _ptr(step.cu_seqlens), _ptr(step.slot_of_seq), _ptr(step.start_pos), _ptr(step.token_seq), _ptr(talk), _ptr(head_bias),
+          _ptr(out), _ptr(partial), n, step.n_seqs, step.max_q_len, n_heads, n_kv, key_dim, value_dim, PAGE, int(ranges),
+          c_float(scale), c_float(softcap), _stream(), kernels=2 if ranges > 1 else 1)

@@ -100,3 +100,49 @@ class ParallelBlock:
             return tuple(pending)
         K.add_dyt(resid, pending, None, None, None, None)     # only the sum into the stream
         return None
+
+
+@register_part("block", "sandwich")
+class SandwichBlock:
+    """Norms before and behind each sublayer: x <- x + m * post1(mixer(pre1(x))), then x <- x + m * post2(ff(pre2(x))); the
+    multiplier m belongs to the norms behind (norm kind "rms_post").  A layer may have no feed-forward.  The norm behind a
+    sublayer is not run by itself: its input travels as a pending output (parts.norm.PostNormed) to the norm that reads
+    the stream next (the next sublayer's, the next block's, or the model's last), whose kernel norms it, adds it and
+    norms the sum."""
+    family = "block"
+    graph_safe = True
+
+    NAMES = ("mixer_norm", "mixer", "mixer_post_norm", "feed_forward_norm", "feed_forward", "feed_forward_post_norm")
+
+    def __init__(self, parts: dict):
+        if not set(self.NAMES[:3]) <= set(parts) <= set(self.NAMES) or len(parts) not in (3, 6):
+            raise ValueError(f"the sandwich block arranges parts named {self.NAMES} (the last three may be absent); the layer has {sorted(parts)}")
+        self.mixer_norm, self.mixer, self.mixer_post = parts["mixer_norm"], parts["mixer"], parts["mixer_post_norm"]
+        self.ff_norm, self.ff, self.ff_post = (parts.get("feed_forward_norm"), parts.get("feed_forward"),
+                                               parts.get("feed_forward_post_norm"))
+        for norm in (self.mixer_norm, self.ff_norm):
+            if norm is not None and not getattr(norm, "takes_post_normed", False):
+                raise ValueError("the norms in front of a sandwich block's sublayers must take a pending normed output")
+
+    def first_norm(self):
+        return self.mixer_norm
+
+    @staticmethod
+    def _pending(post, result):
+        """A sublayer returns its output, or (output, bias) when its last product's bias is still to be added."""
+        if isinstance(result, tuple):
+            return post.pending(result[0], result[1])
+        return post.pending(result)
+
+    def forward(self, resid, delta, step, cache_view, next_norm=None):
+        if getattr(step, "handoff", None) is not None:
+            step.handoff.expect(None)          # no product of this block prepares a norm's input
+        h = self.mixer_norm.add_norm(resid, delta)
+        pending = self._pending(self.mixer_post, self.mixer.forward(h, step, cache_view))
+        if self.ff is not None:
+            h = self.ff_norm.add_norm(resid, pending)
+            pending = self._pending(self.ff_post, self.ff.forward(h, step))
+        if getattr(next_norm, "takes_post_normed", False):
+            return pending
+        self.mixer_post.add(resid, pending)
+        return None

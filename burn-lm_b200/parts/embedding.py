@@ -54,6 +54,31 @@ class Embedding(Part):
 
 
 @dataclass(frozen=True)
+class ScaledEmbeddingSpec:
+    vocab_size: int
+    hidden_size: int
+    scale: float
+
+
+@register_part("embedding", "scaled_table")
+class ScaledEmbedding(Part):
+    """x = table[token] * scale, the product taken in fp32; the table itself stays as stored (a tied head reads it unscaled)."""
+    family = "embedding"
+    graph_safe = True
+    roles = ("table",)
+    kernel_modules = ("stream_ops",)
+
+    def tensor_specs(self):
+        return [TensorSpec(self.tensor_names["table"], (self.spec.vocab_size, self.spec.hidden_size))]
+
+    def bind(self, loaded):
+        self.table = loaded[self.tensor_names["table"]]
+
+    def forward(self, tokens, out):
+        K.embed_scaled(tokens, self.table, out, self.spec.scale)
+
+
+@dataclass(frozen=True)
 class PairEmbeddingSpec:
     vocab_size: int
     hidden_size: int

@@ -1,4 +1,5 @@
-"""Norms fused with the residual add: RMS norm, and Dynamic Tanh (which takes no statistics).
+"""Norms fused with the residual add: RMS norm, Dynamic Tanh (which takes no statistics), and the RMS norm that
+stands behind a sublayer and scales what it adds to the stream.
 
 y = x / sqrt(mean(x^2) + eps) * gamma; it stands before the mixer, before the feed-forward and once
 after the last block (crates/burn-lm-llama/src/nn/transformer.rs:248-255,101; eps at :60-62 and
@@ -7,6 +8,7 @@ after the last block (crates/burn-lm-llama/src/nn/transformer.rs:248-255,101; ep
 from __future__ import annotations
 
 from dataclasses import dataclass
+from typing import Optional
 
 import torch
 
@@ -23,6 +25,18 @@ class RMSNormSpec:
     eps: float
 
 
+@dataclass
+class PostNormed:
+    """A sublayer's raw output that is still to be normed, scaled and added to the stream:
+    stream += mult * (output (+ bias)) / rms(output (+ bias)) * weight.  The norm that reads the stream next does it in
+    its own kernel (a norm with `takes_post_normed`), or `PostRMSNorm.add` does it alone."""
+    output: torch.Tensor          # [N, D] float32 or the compute dtype
+    weight: torch.Tensor          # float32 [D]
+    eps: float
+    mult: float
+    bias: Optional[torch.Tensor] = None     # float32 [D]: a bias of the sublayer's last product, not added yet
+
+
 @register_part("norm", "rmsnorm")
 class RMSNorm(Part):
     family = "norm"
@@ -36,11 +50,22 @@ class RMSNorm(Part):
         self.gamma = loaded[self.tensor_names["weight"]]
 
     takes_handed_norm = True      # a product that writes the stream may leave this norm's input (parts.linear.NormHandoff)
+    takes_post_normed = True      # `delta` may be a PostNormed: normed, scaled and added by this norm's kernel
 
     def add_norm(self, resid, delta, rows=None, lazy=False, handoff=None):
         """`lazy`: the caller can take a norm that is not computed yet (parts.linear.NormedStream);
         it gets one when nothing has to be added into the stream first.  `handoff`: where the writer of
         the stream may have left this norm's input."""
+        if isinstance(delta, PostNormed):
+            if handoff is not None:
+                handoff.claim(resid, self.gamma)          # nothing a product left fits a stream that changes now
+            n = rows.numel() if rows is not None else resid.shape[0]
+            out = torch.empty((n, self.spec.size), dtype=self.runtime.dtype, device=resid.device)
+            if getattr(self, "_gamma32", None) is None:
+                self._gamma32 = self.gamma.to(torch.float32).contiguous()
+            K.sandwich_norm(resid, delta.output, delta.weight, delta.mult, delta.eps, self._gamma32, self.spec.eps, out,
+                            rows=rows, delta_bias=delta.bias)
+            return out
         handed = handoff.claim(resid, self.gamma) if handoff is not None else None
         if lazy and delta is None:
             return NormedStream(resid, self.gamma, self.spec.eps, rows, self.runtime.dtype, handed)
@@ -48,6 +73,37 @@ class RMSNorm(Part):
         out = torch.empty((n, self.spec.size), dtype=self.runtime.dtype, device=resid.device)
         K.add_rmsnorm(resid, delta, self.gamma, self.spec.eps, out, rows)
         return out
+
+
+@dataclass(frozen=True)
+class PostRMSNormSpec:
+    size: int
+    eps: float
+    mult: float = 1.0             # what the normed output is multiplied by before it joins the stream
+
+
+@register_part("norm", "rms_post")
+class PostRMSNorm(Part):
+    """The RMS norm behind a sublayer: x <- x + mult * norm(sublayer output).  It computes nothing by itself: `pending`
+    wraps the output for the norm that reads the stream next, which adds and norms in one kernel."""
+    family = "norm"
+    graph_safe = True
+    roles = ("weight",)
+    kernel_modules = ("stream_ops",)
+
+    def tensor_specs(self):
+        return [TensorSpec(self.tensor_names["weight"], (self.spec.size,), init="one_plus_normal:0.1")]
+
+    def bind(self, loaded):
+        self.weight = loaded[self.tensor_names["weight"]].to(torch.float32).contiguous()
+
+    def pending(self, output, bias=None) -> PostNormed:
+        return PostNormed(output, self.weight, self.spec.eps, self.spec.mult, bias)
+
+    @staticmethod
+    def add(resid, pending: PostNormed) -> None:
+        """Only the add into the stream (no norm reads it next)."""
+        K.sandwich_norm(resid, pending.output, pending.weight, pending.mult, pending.eps, None, 0.0, None, delta_bias=pending.bias)
 
 
 @dataclass(frozen=True)

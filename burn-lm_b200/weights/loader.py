@@ -41,6 +41,14 @@ class TensorSpec:
     init: str = "normal:0.02"    # for the random-weights mode: "normal:<std>" or "one_plus_normal:<std>"
     optional: bool = False       # a tensor the format stores but the part does not read: loaded when it is there,
                                  # not missed when it is not (the random-weights mode writes it)
+    free: int = 0                # a dimension given as -1 is read off the stored tensor (a size that no configuration key
+                                 # names); the random-weights mode makes it this large
+
+
+def shape_fits(wanted, stored) -> bool:
+    """Whether a stored shape is the wanted one; a wanted dimension of -1 takes any size."""
+    wanted, stored = tuple(wanted), tuple(stored)
+    return len(wanted) == len(stored) and all(w == -1 or w == g for w, g in zip(wanted, stored))
 
 
 def _open_folder(folder: str) -> list[SafetensorsFile]:
@@ -97,7 +105,7 @@ def load_tensors(folder: str, specs: list, compute_dtype: torch.dtype, device, i
         for n, s in wanted.items():
             if n in where:
                 f = where[n]
-                if tuple(f.shape(n)) != tuple(s.shape):
+                if not shape_fits(s.shape, f.shape(n)):
                     wrong.append((n, tuple(s.shape), tuple(f.shape(n))))
                 elif (s.kind == "int") == f.dtype(n).is_floating_point:
                     wrong.append((n, f"{s.kind} table", str(f.dtype(n))))

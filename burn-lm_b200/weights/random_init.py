@@ -32,7 +32,10 @@ def random_tensor(spec, seed: int, dtype: torch.dtype, device="cpu") -> torch.Te
     std = float(arg)
     g = torch.Generator(device=device)
     g.manual_seed(tensor_seed(seed, spec.name))
-    t = torch.empty(tuple(spec.shape), dtype=torch.float32, device=device)
+    shape = tuple(spec.free if d == -1 else d for d in spec.shape)     # a size no key names: the spec's own choice
+    if any(d < 1 for d in shape) and len(shape) > 0:
+        raise ValueError(f"tensor {spec.name!r}: no size to make the free dimension of {tuple(spec.shape)}")
+    t = torch.empty(shape, dtype=torch.float32, device=device)
     t.normal_(0.0, std, generator=g)
     if kind == "one_plus_normal":
         t += 1.0
