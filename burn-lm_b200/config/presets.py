@@ -82,6 +82,35 @@ _PRESETS["fobilorn_tiny"] = {
 }
 
 
+def _nufolix_parallel(heads, kv_heads, dim, vdim, rot_dims, r_heads, r_qk_heads, r_dim, r_vdim, r_conv, ff, left_scale=0.5,
+                      right_scale=1.25, softcap=15.0, base=10000.0, scale=None):
+    return {"type": "parallel", "mlp": {"kind": "dense", "ff": ff} if ff else None,
+            "mixer": {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale or dim ** -0.5,
+                               "softcap": softcap, "rot": {"dims": rot_dims, "base": base}},
+                      "right": {"heads": r_heads, "kv_heads": r_qk_heads, "dim": r_dim, "vdim": r_vdim, "conv": r_conv},
+                      "left_scale": left_scale, "right_scale": right_scale}}
+
+
+def _nufolix_mamba2(heads, vdim, state, groups, conv, norm_groups, ff):
+    return {"type": "mamba2", "mlp": {"kind": "dense", "ff": ff} if ff else None,
+            "mixer": {"heads": heads, "vdim": vdim, "state": state, "groups": groups, "conv": conv, "norm_groups": norm_groups}}
+
+
+# a small Nufolix decoder that uses every branch of the design: both kinds of mixer with and without a feed-forward,
+# several query heads a key/value head on both sides of the parallel mixer, a rotation of some of a head's lanes,
+# state-space heads that share their B and C in groups, a norm in several parts
+_PRESETS["nufolix_tiny"] = {
+    "architecture": "Nufolix", "vocab": 320, "width": 96, "embedding": {"scale": 9.797958971132712}, "norm": {"eps": 1e-5},
+    "residual_mult": 0.8,
+    "layers": [
+        _nufolix_mamba2(6, 16, 24, 2, 4, 3, None),
+        _nufolix_parallel(4, 2, 24, 16, 16, 4, 2, 16, 24, 3, 160),
+        _nufolix_mamba2(4, 24, 16, 4, 3, 1, 128),
+        _nufolix_parallel(6, 3, 16, 32, 8, 2, 1, 32, 16, 4, None),
+    ],
+}
+
+
 def preset_names() -> list:
     return sorted(_PRESETS)
 

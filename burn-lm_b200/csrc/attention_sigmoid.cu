@@ -4,7 +4,7 @@
 //     m_h(i, j) = sum_g talk[h, g] w_g(i, j)                              (talk null: m = w)
 //     out_h(i)  = sum_j m_h(i, j) v_cj
 // and the kernel in front of it: projection bias, rotation of the first `rot` lanes of every q and k head (lane i
-// with lane i + rot / 2, angle = position * freq[i] in fp32), append of k and v to the paged cache.
+// with lane i + rot / 2, angle = position * freq[i], taken in fp64 and applied in fp32), append of k and v to the paged cache.
 // Scores, weights, the mix and the sums over keys are fp32 in both dtypes.
 //
 // Because nothing normalises over the keys, a query's keys can be cut into ranges whose partial outputs simply add:
@@ -24,7 +24,7 @@ constexpr int kThreads = 256;
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void bias_rope_append_kernel(const float* __restrict__ proj, long long stride, const float* __restrict__ bias,
-                                        const float* __restrict__ freq, int rot, T* __restrict__ q_out, T* __restrict__ pool,
+                                        const double* __restrict__ freq, int rot, T* __restrict__ q_out, T* __restrict__ pool,
                                         const int* __restrict__ token_seq, const int* __restrict__ token_pos,
                                         const int* __restrict__ slot_of_seq, const int* __restrict__ block_table, int table_stride,
                                         int H, int G, int dk, int dv, int page) {
@@ -45,8 +45,9 @@ __global__ void bias_rope_append_kernel(const float* __restrict__ proj, long lon
             const int i = lane < half ? lane : lane - half;
             const int pe = lane < half ? e + half : e - half;
             const float other = row[pe] + (bias ? bias[pe] : 0.f);
-            float s, c;
-            sincosf((float)pos * freq[i], &s, &c);
+            double sd, cd;
+            sincos((double)pos * freq[i], &sd, &cd);     // the angle and its sine and cosine in fp64, applied in fp32
+            const float s = (float)sd, c = (float)cd;
             val = lane < half ? val * c - other * s : val * c + other * s;
         }
         if (head < H) {
@@ -67,7 +68,7 @@ __global__ void bias_rope_append_kernel(const float* __restrict__ proj, long lon
     else base[(size_t)G * page * dk + ((size_t)head * page + at) * dv + lane] = from_f32<T>(val);
 }
 
-BLM_API int blm_bias_rope_append(const float* proj, long long stride, const float* bias, const float* freq, int rot, void* q_out,
+BLM_API int blm_bias_rope_append(const float* proj, long long stride, const float* bias, const double* freq, int rot, void* q_out,
                                  void* pool, int dtype, const int* token_seq, const int* token_pos, const int* slot_of_seq,
                                  const int* block_table, int table_stride, int n, int H, int G, int dk, int dv, int page,
                                  cudaStream_t stream) {

@@ -1106,10 +1106,11 @@ def gated_group_norm(y, gate, gate_col0, weight, group, mode, eps, out):
 # ------------------------------------------------------------------------------------------------
 def bias_rope_append(proj, bias, freq, rotary_dim, q_out, pool, block_table, step, n_heads, n_kv, key_dim, value_dim):
     """proj float32 [N, q | k | v] (+ bias float32): the first rotary_dim lanes of every q and k head are rotated (lane i
-    with lane i + rotary_dim / 2 by position * freq[i], freq float32 [rotary_dim / 2], the angle in fp32); q goes to q_out
+    with lane i + rotary_dim / 2 by position * freq[i], freq float64 [rotary_dim / 2]; the angle, its sine and its cosine are
+    taken in fp64 and applied in fp32); q goes to q_out
     [N, n_heads * key_dim], k and v to the token's place in the paged cache."""
     _need_cuda(proj, bias, freq, q_out, pool, block_table)
-    _f32(proj, bias, freq)
+    _f32(proj, bias)
     n = step.n_tokens
     width = (n_heads + n_kv) * key_dim + n_kv * value_dim
     if proj.dim() != 2 or proj.shape[0] != n or proj.shape[1] != width or (bias is not None and bias.numel() != width):
@@ -1118,8 +1119,8 @@ def bias_rope_append(proj, bias, freq, rotary_dim, q_out, pool, block_table, ste
         raise KernelError("bias_rope_append: q_out [N, heads * key_dim] in the cache's dtype")
     if pool.numel() % kv_page_elems(n_kv, key_dim, value_dim):
         raise KernelError("bias_rope_append: the pool does not consist of pages of keys [kv, PAGE, key_dim] and values [kv, PAGE, value_dim]")
-    if rotary_dim and (freq is None or freq.numel() != rotary_dim // 2):
-        raise KernelError("bias_rope_append: freq must be float32 [rotary_dim / 2]")
+    if rotary_dim and (freq is None or freq.dtype != torch.float64 or freq.numel() != rotary_dim // 2):
+        raise KernelError("bias_rope_append: freq must be float64 [rotary_dim / 2]")
     _call("attention_sigmoid", "blm_bias_rope_append", _ptr(proj), c_longlong(proj.stride(0)), _ptr(bias), _ptr(freq), int(rotary_dim),
           _ptr(q_out), _ptr(pool), _code(pool.dtype), _ptr(step.token_seq), _ptr(step.token_pos), _ptr(step.slot_of_seq),
           _ptr(block_table), block_table.shape[1], n, n_heads, n_kv, key_dim, value_dim, PAGE, _stream())

@@ -1,7 +1,7 @@
 """Attention without a softmax, whose heads' weights are mixed before they meet the values.
 
 q = Wq h + bq, k = Wk h + bk, v = Wv h + bv; the first `rotary_dim` lanes of every q and k head are rotated (lane i
-with lane i + rotary_dim / 2, angle position * base^(-2i / rotary_dim), the angle taken in fp32); query head h reads
+with lane i + rotary_dim / 2, angle position * base^(-2i / rotary_dim), taken in fp64 and applied in fp32); query head h reads
 key/value head h // (heads / kv heads); keys have `head_dim` lanes and values `value_dim`.  s = scale q.k, then
 softcap tanh(s / softcap) when a cap is set; the weight of a visible key (j <= i) is sigmoid(s + head_bias_h), not
 normalised over the keys; weights are mixed across heads, w'_h = sum_g talk[h, g] w_g, and head h applies w'_h to the
@@ -57,7 +57,7 @@ class SigmoidAttention(Part):
             raise ValueError(f"{s.rotary_dim} rotated lanes: an even number of at most head_dim {s.head_dim}")
         half = s.rotary_dim // 2
         self.freq = torch.tensor([s.rotary_base ** (-2.0 * i / s.rotary_dim) for i in range(half)], dtype=torch.float64) \
-            .to(torch.float32).to(runtime.device) if half else None
+            .to(runtime.device) if half else None
 
     def tensor_specs(self):
         s, t = self.spec, self.tensor_names
