@@ -1,7 +1,7 @@
 """Decode and prefill throughput of the Llama-3.2-1B shape with random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--config 1b|3b|8b]
-    python bench.py --compare fobilorn [--size 1b-layers|8b-layers]     (another design beside this one, see run_compare)
+    python bench.py --compare fobilorn|nufolix [--size 1b-layers|8b-layers]     (another design beside this one, see run_compare)
 
 A "step" is one decode step of the whole batch.  The default run has the layer sizes of the 1B
 configuration (16 layers, width 2048, 32 heads on 8 kv heads of 64, inner 8192, vocabulary 128256,
@@ -397,6 +397,101 @@ def compare_kernels(z, pk):
     return out
 
 
+def nufolix_configs(z):
+    """(llama, nufolix) of one size: half of the new design's layers are state-space scans without a feed-forward, half hold
+    sigmoid attention beside a gated delta rule and a dense feed-forward of the same inner size as the dense decoder's."""
+    llama = compare_configs(z)["llama"]
+    hd, d = z["hd"], z["width"]
+    par = {"type": "parallel", "mlp": {"kind": "dense", "ff": z["inner"]},
+           "mixer": {"left": {"heads": z["heads"], "kv_heads": z["kv"], "dim": hd, "vdim": hd, "scale": hd ** -0.5, "softcap": 30.0,
+                              "rot": {"dims": hd, "base": 500000.0}},
+                     "right": {"heads": d // 128, "kv_heads": d // 256, "dim": 128, "vdim": 128, "conv": 4},
+                     "left_scale": 0.7, "right_scale": 0.7}}
+    ssm = {"type": "mamba2", "mlp": None,
+           "mixer": {"heads": 2 * d // 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 8}}
+    nuf = {"architecture": "Nufolix", "vocab": z["vocab"], "width": d, "embedding": {"scale": d ** 0.5}, "norm": {"eps": 1e-6},
+           "residual_mult": 0.7, "layers": [par if i % 2 == 0 else ssm for i in range(z["layers"])]}
+    return {"llama": llama, "nufolix": nuf}
+
+
+def nufolix_kernels(z, pk):
+    """The new design's kernels alone, CUDA events, back to back, beside the like kernel of the dense decoder where it has
+    one: attention over one 2,048-token prompt and over 64 sequences of 1,088 tokens, the two scans over the same rows."""
+    import torch
+    from types import SimpleNamespace
+    from burn_lm_b200 import kernels as K
+    dev, bf = "cuda", torch.bfloat16
+    H, G, hd, d = z["heads"], z["kv"], z["hd"], z["width"]
+    out = {}
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+
+    def step(n_seqs, new, cached):
+        seq = [s for s in range(n_seqs) for _ in range(new)]
+        pos = [cached + t for _ in range(n_seqs) for t in range(new)]
+        return SimpleNamespace(token_seq=i32(seq), token_pos=i32(pos), slot_of_seq=i32(list(range(n_seqs))),
+                               cu_seqlens=i32([new * s for s in range(n_seqs + 1)]), start_pos=i32([cached] * n_seqs),
+                               n_tokens=n_seqs * new, n_seqs=n_seqs, max_q_len=new, max_kv_len=cached + new)
+
+    def attention_case(n_seqs, new, cached, ranges):
+        total = cached + new
+        pages_each = -(-total // K.PAGE)
+        n = n_seqs * new
+        bt = torch.arange(n_seqs * pages_each, dtype=torch.int32, device=dev).reshape(n_seqs, pages_each)
+        st = step(n_seqs, new, cached)
+        q = torch.randn((n, H * hd), dtype=bf, device=dev)
+        pool5 = torch.randn((n_seqs * pages_each, 2, G, K.PAGE, hd), dtype=bf, device=dev)
+        o = torch.empty_like(q)
+        ms_llama = _time(lambda: K.attention(q, q.shape[1], pool5, bt, st.cu_seqlens, st.slot_of_seq, st.start_pos, o, n, n_seqs, new,
+                                             H, G, hd, hd ** -0.5, window=0, n_splits=1, max_kv_len=total))
+        pool = pool5.reshape(n_seqs * pages_each, -1)
+        talk = torch.randn((H, H), dtype=torch.float32, device=dev) * 0.2
+        pb = torch.randn(H, dtype=torch.float32, device=dev) - 3.0
+        partial = torch.empty(ranges * n * H * hd, dtype=torch.float32, device=dev) if ranges > 1 else None
+        ms_new = _time(lambda: K.sigmoid_attention(q, pool, bt, st, o, H, G, hd, hd, hd ** -0.5, softcap=30.0, talk=talk, head_bias=pb,
+                                                   ranges=ranges, partial=partial), reps=3)
+        return ms_llama, ms_new, total
+
+    ms_l, ms_n, total = attention_case(1, 2048, 0, 1)
+    pairs = 2048 * 2049 / 2
+    flops = 4.0 * H * hd * pairs
+    mix = 2.0 * H * H * pairs                      # the heads' mix: fp32 multiply-adds outside the tensor cores
+    out["attention_prefill_2048"] = {"llama_ms": round(ms_l, 4), "nufolix_ms": round(ms_n, 4), "mix_gflop_fp32": round(mix / 1e9, 1),
+                                     "llama_frac_bf16": round(flops / (ms_l / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+                                     "nufolix_frac_bf16": round(flops / (ms_n / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+    ms_l, ms_n, total = attention_case(64, 1, 1087, 4)
+    nbytes = 64 * G * total * 2 * hd * 2
+    out["attention_decode_b64"] = {"llama_ms": round(ms_l, 4), "nufolix_ms": round(ms_n, 4), "keys_seen": total,
+                                   "llama_frac_hbm": round(nbytes / (ms_l / 1e3) / 1e9 / pk["hbm_gbs"], 4),
+                                   "nufolix_frac_hbm": round(nbytes / (ms_n / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
+    # the scans: prompts read and write rows (a pass over their inputs and outputs), single tokens the states
+    for name, heads, groups, rows, dv in (("ssm", 2 * d // 64, 8, 128, 64), ("delta", d // 128, d // 256, 128, 128)):
+        inner = heads * dv
+        for n_seqs, new, cached in ((1, 2048, 0), (64, 1, 1087)):
+            st = step(n_seqs, new, cached)
+            n = st.n_tokens
+            floats = K.scan_state_floats(heads, rows, dv)
+            state = torch.zeros((n_seqs, 2, floats), dtype=torch.float32, device=dev)
+            y = torch.zeros((n, inner), dtype=torch.float32, device=dev)
+            if name == "ssm":
+                xbc = torch.randn((n, inner + 2 * groups * rows), dtype=torch.float32, device=dev)
+                dt = torch.randn((n, heads), dtype=torch.float32, device=dev)
+                one = torch.zeros(heads, dtype=torch.float32, device=dev)
+                ms = _time(lambda: K.ssm_scan(xbc, 0, inner, inner + groups * rows, dt, 0, one, one, one, y, heads, groups, rows, dv, st, state, 0), reps=3)
+                row_bytes = 4.0 * n * (2 * inner + 2 * groups * rows + heads)
+            else:
+                qkv = torch.randn((n, 2 * groups * rows + inner), dtype=torch.float32, device=dev)
+                b = torch.randn((n, heads), dtype=torch.float32, device=dev)
+                a = torch.randn((n, heads * rows), dtype=torch.float32, device=dev)
+                bias, alog = torch.zeros(heads * rows, dtype=torch.float32, device=dev), torch.zeros(heads, dtype=torch.float32, device=dev)
+                ms = _time(lambda: K.delta_scan(qkv, 0, qkv, groups * rows, qkv, 2 * groups * rows, b, 0, a, 0, bias, alog, y, heads, groups, rows, dv, st, state, 0), reps=3)
+                row_bytes = 4.0 * n * (2 * inner + 2 * groups * rows + heads * rows + heads)
+            state_bytes = 2.0 * 4 * n_seqs * floats          # read and written once a step
+            flops = (4.0 if name == "ssm" else 8.0) * n * heads * rows * dv
+            out[f"{name}_scan_{n_seqs}x{new}"] = {"ms": round(ms, 4), "frac_hbm": round((row_bytes + state_bytes) / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4),
+                                                  "gflop_fp32_per_s": round(flops / (ms / 1e3) / 1e9, 1)}
+    return out
+
+
 def run_compare(args):
     """One JSON line per size and model: prefill of one 2,048-token prompt and decode at batch 8 and 64 after 512-token
     prompts, for the dense Llama decoder and the Fobilorn decoder (dense feed-forwards, and experts) at equal layer
@@ -410,7 +505,8 @@ def run_compare(args):
     for size, z in COMPARE_SIZES.items():
         if args.size and size != args.size:
             continue
-        for name, cfg in compare_configs(z).items():
+        configs = nufolix_configs(z) if args.compare == "nufolix" else compare_configs(z)
+        for name, cfg in configs.items():
             vocab = z["vocab"]
             lm = blm.load_random(cfg, seed=0, dtype="bfloat16", max_seq_len=4096, max_batch=64, max_tokens=64 * 1024)
             engine = lm.engine
@@ -426,7 +522,8 @@ def run_compare(args):
             print(json.dumps(line), flush=True)
             del lm, engine
             torch.cuda.empty_cache()
-        print(json.dumps({"compare": size, "kernels": compare_kernels(z, pk), "peaks": pk["source"]}), flush=True)
+        alone = nufolix_kernels(z, pk) if args.compare == "nufolix" else compare_kernels(z, pk)
+        print(json.dumps({"compare": size, "kernels": alone, "peaks": pk["source"]}), flush=True)
     return 0
 
 
@@ -540,7 +637,7 @@ def main():
     ap.add_argument("--only", default=None, choices=["decode", "prefill", "sweep"],
                     help="run one workload briefly (for profilers), or a sweep over batch sizes and context lengths")
     ap.add_argument("--prompt-tokens", type=int, default=0, help="with --only prefill: one prompt of this many tokens instead of the workload's")
-    ap.add_argument("--compare", default=None, choices=["fobilorn"],
+    ap.add_argument("--compare", default=None, choices=["fobilorn", "nufolix"],
                     help="instead of the workload: the named design beside the dense Llama decoder at equal layer sizes "
                          "(prefill and decode throughput, then its kernels alone), one JSON line each")
     ap.add_argument("--size", default=None, choices=sorted(COMPARE_SIZES), help="with --compare: one of the sizes only")

@@ -251,6 +251,240 @@ __global__ void __launch_bounds__(kThreads) sigmoid_attn_kernel(const SigmoidAtt
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same attention on the tensor cores (bfloat16, prompts): 16 query rows of one sequence a block, all heads' scores by
+// mma.sync m16n8k16 (Q rows x a chunk of keys), the weights and their mix in fp32 on the CUDA cores, the mixed weights
+// rounded to bfloat16 for the second product with the values.  Heads are cut into grid.z groups for the second product
+// only (every block needs every head's weights for the mix), so that a block's outputs fit its registers.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void ldsm_x4(unsigned (&r)[4], const void* p) {
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2(unsigned (&r)[2], const void* p) {
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2_trans(unsigned (&r)[2], const void* p) {
+    const unsigned addr = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], const unsigned (&a)[4], const unsigned (&b)[2]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+constexpr int kRows = 16;          // query rows of a block of the tensor-core kernel
+
+struct MmaLayout {                 // strides and offsets (bytes) of the block's shared memory
+    int dkp, dvp, kvp, ssp, msp, hown, hpad;
+    size_t ts, pbs, ss, ms, qs, kv, total;
+};
+
+__host__ __device__ inline MmaLayout mma_layout(int H, int G, int dk, int dv, int KC, int HG) {
+    MmaLayout l;
+    l.dkp = dk + 8;
+    l.dvp = dv + 8;
+    l.kvp = l.dkp > l.dvp ? l.dkp : l.dvp;
+    l.ssp = KC + 8;                                     // floats a row of weights
+    l.msp = KC + 8;                                     // bfloat16 a row of mixed weights
+    l.hown = H / HG;
+    l.hpad = (l.hown + 7) / 8 * 8;
+    l.ts = 0;                                           // [H][hpad] floats: talk transposed, own heads by columns
+    l.pbs = l.ts + (size_t)H * l.hpad * 4;              // [H] floats
+    l.ss = l.pbs + (size_t)((H + 3) / 4 * 4) * 4;       // [H][16][ssp] floats
+    l.ms = l.ss + (size_t)H * kRows * l.ssp * 4;        // [hown][16][msp] bfloat16
+    l.qs = l.ms + (size_t)l.hown * kRows * l.msp * 2;   // [H][16][dkp] bfloat16
+    l.kv = l.qs + (size_t)H * kRows * l.dkp * 2;        // [G][KC][kvp] bfloat16
+    l.total = l.kv + (size_t)G * KC * l.kvp * 2;
+    return l;
+}
+
+template <int NT>      // 16 x 8 output tiles a warp owns
+__global__ void __launch_bounds__(kThreads) sigmoid_attn_mma_kernel(const SigmoidAttnArgs a, int HG) {
+    typedef __nv_bfloat16 T;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int H = a.H, G = a.G, dk = a.dk, dv = a.dv, KC = a.KC;
+    const MmaLayout L = mma_layout(H, G, dk, dv, KC, HG);
+    float* Ts = reinterpret_cast<float*>(smem_raw + L.ts);
+    float* pbs = reinterpret_cast<float*>(smem_raw + L.pbs);
+    float* Ss = reinterpret_cast<float*>(smem_raw + L.ss);
+    T* Ms = reinterpret_cast<T*>(smem_raw + L.ms);
+    T* Qs = reinterpret_cast<T*>(smem_raw + L.qs);
+    T* KVs = reinterpret_cast<T*>(smem_raw + L.kv);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int seq = blockIdx.x / a.q_tiles, tile = blockIdx.x % a.q_tiles;
+    const int first = a.cu_seqlens[seq];
+    const int n_new = a.cu_seqlens[seq + 1] - first;
+    const int i0 = tile * kRows;
+    if (i0 >= n_new) return;
+    const int nq = min(kRows, n_new - i0);
+    const int start = a.start_pos[seq];
+    const int kv_hi = start + i0 + nq;
+    const int chunks = (kv_hi + KC - 1) / KC;
+    const int per = (chunks + a.ranges - 1) / a.ranges;
+    const int c_lo = blockIdx.y * per, c_hi = min(chunks, c_lo + per);
+    const int* table = a.block_table + (size_t)a.slot_of_seq[seq] * a.table_stride;
+    const int per_kv = H / G;
+    const int HD = H * dv;
+    const int h0 = blockIdx.z * L.hown;                 // this block's heads for the second product
+    const int dv8 = dv / 8;
+    const int own_tiles = L.hown * dv8;
+
+    for (int e = tid; e < H * L.hpad; e += kThreads) {
+        const int g = e / L.hpad, hl = e % L.hpad;
+        Ts[e] = hl < L.hown ? (a.talk ? a.talk[(size_t)(h0 + hl) * H + g] : (h0 + hl == g ? 1.f : 0.f)) : 0.f;
+    }
+    for (int e = tid; e < H; e += kThreads) pbs[e] = a.head_bias ? a.head_bias[e] : 0.f;
+    const T* q = reinterpret_cast<const T*>(a.q);
+    const int dk8 = dk / 8;
+    for (int e = tid; e < H * kRows * dk8; e += kThreads) {          // 16-byte pieces of the tile's queries
+        const int c = e % dk8, i = (e / dk8) % kRows, h = e / (dk8 * kRows);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (i < nq) v = *reinterpret_cast<const uint4*>(q + (size_t)(first + i0 + i) * H * dk + h * dk + c * 8);
+        *reinterpret_cast<uint4*>(Qs + (size_t)(h * kRows + i) * L.dkp + c * 8) = v;
+    }
+    float acc[NT][4];
+#pragma unroll
+    for (int x = 0; x < NT; ++x) acc[x][0] = acc[x][1] = acc[x][2] = acc[x][3] = 0.f;
+    const T* pool = reinterpret_cast<const T*>(a.pool);
+    const size_t page_elems = (size_t)G * a.page * (dk + dv);
+    const bool cap = a.softcap > 0.f;
+    const float inv_cap = cap ? 1.0f / a.softcap : 0.f;
+    const int n_tiles_s = H * (KC / 8);                  // score tiles of a chunk: (head, 8 keys)
+
+    for (int ch = c_lo; ch < c_hi; ++ch) {
+        const int j0 = ch * KC;
+        const T* pg = pool + (size_t)table[j0 / a.page] * page_elems;
+        const int at0 = j0 % a.page;
+        __syncthreads();
+        for (int e = tid; e < G * KC * dk8; e += kThreads) {
+            const int c = e % dk8, j = (e / dk8) % KC, g = e / (dk8 * KC);
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (j0 + j < kv_hi) v = *reinterpret_cast<const uint4*>(pg + ((size_t)g * a.page + at0 + j) * dk + c * 8);
+            *reinterpret_cast<uint4*>(KVs + (size_t)(g * KC + j) * L.dkp + c * 8) = v;
+        }
+        __syncthreads();
+        // scores of all heads on the tensor cores, weights in fp32
+        for (int s = warp; s < n_tiles_s; s += kThreads / 32) {
+            const int h = s / (KC / 8), nt = s % (KC / 8);
+            float c4[4] = {0.f, 0.f, 0.f, 0.f};
+            const T* qa = Qs + (size_t)(h * kRows + (lane & 15)) * L.dkp + (lane >> 4) * 8;
+            const T* kb = KVs + (size_t)((h / per_kv) * KC + nt * 8 + (lane & 7)) * L.dkp + ((lane >> 3) & 1) * 8;
+            for (int kk = 0; kk < dk; kk += 16) {
+                unsigned af[4], bf[2];
+                ldsm_x4(af, qa + kk);
+                ldsm_x2(bf, kb + kk);
+                mma_16816(c4, af, bf);
+            }
+            const float pb = pbs[h];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const int i = (lane >> 2) + 8 * r;
+                float w2[2];
+#pragma unroll
+                for (int cc = 0; cc < 2; ++cc) {
+                    const int j = nt * 8 + 2 * (lane & 3) + cc;
+                    float w = 0.f;
+                    if (i < nq && j0 + j <= start + i0 + i) {
+                        float sc = c4[2 * r + cc] * a.scale;
+                        if (cap) sc = a.softcap * tanhf(sc * inv_cap);
+                        w = 1.0f / (1.0f + expf(-(sc + pb)));
+                    }
+                    w2[cc] = w;
+                }
+                *reinterpret_cast<float2*>(Ss + (size_t)(h * kRows + i) * L.ssp + nt * 8 + 2 * (lane & 3)) = make_float2(w2[0], w2[1]);
+            }
+        }
+        __syncthreads();
+        // the values take the keys' place while the weights of this block's heads are mixed
+        for (int e = tid; e < G * KC * dv8; e += kThreads) {
+            const int c = e % dv8, j = (e / dv8) % KC, g = e / (dv8 * KC);
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (j0 + j < kv_hi) v = *reinterpret_cast<const uint4*>(pg + (size_t)G * a.page * dk + ((size_t)g * a.page + at0 + j) * dv + c * 8);
+            *reinterpret_cast<uint4*>(KVs + (size_t)(g * KC + j) * L.dvp + c * 8) = v;
+        }
+        for (int e = tid; e < (L.hpad / 8) * kRows * KC; e += kThreads) {
+            const int j = e % KC, i = (e / KC) % kRows, hc = e / (KC * kRows);
+            float m[8];
+#pragma unroll
+            for (int x = 0; x < 8; ++x) m[x] = 0.f;
+            const float* sp = Ss + (size_t)i * L.ssp + j;
+            const float* tp = Ts + hc * 8;
+            for (int g = 0; g < H; ++g) {
+                const float sv = sp[(size_t)g * kRows * L.ssp];
+                const float4 t0 = *reinterpret_cast<const float4*>(tp + (size_t)g * L.hpad);
+                const float4 t1 = *reinterpret_cast<const float4*>(tp + (size_t)g * L.hpad + 4);
+                m[0] += t0.x * sv; m[1] += t0.y * sv; m[2] += t0.z * sv; m[3] += t0.w * sv;
+                m[4] += t1.x * sv; m[5] += t1.y * sv; m[6] += t1.z * sv; m[7] += t1.w * sv;
+            }
+#pragma unroll
+            for (int x = 0; x < 8; ++x)
+                if (hc * 8 + x < L.hown) Ms[(size_t)((hc * 8 + x) * kRows + i) * L.msp + j] = __float2bfloat16_rn(m[x]);
+        }
+        __syncthreads();
+        // mixed weights x values
+#pragma unroll
+        for (int x = 0; x < NT; ++x) {
+            const int t = warp * NT + x;
+            if (t < own_tiles) {
+                const int hl = t / dv8, nt = t % dv8;
+                const T* ma = Ms + (size_t)(hl * kRows + (lane & 15)) * L.msp + (lane >> 4) * 8;
+                const T* vb = KVs + (size_t)(((h0 + hl) / per_kv) * KC + (lane & 15)) * L.dvp + nt * 8;
+                for (int kk = 0; kk < KC; kk += 16) {
+                    unsigned af[4], bf[2];
+                    ldsm_x4(af, ma + kk);
+                    ldsm_x2_trans(bf, vb + (size_t)kk * L.dvp);
+                    mma_16816(acc[x], af, bf);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int x = 0; x < NT; ++x) {
+        const int t = warp * NT + x;
+        if (t < own_tiles) {
+            const int hl = t / dv8, nt = t % dv8;
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const int i = (lane >> 2) + 8 * r;
+                if (i < nq) {
+                    const size_t at = (size_t)(first + i0 + i) * HD + (h0 + hl) * dv + nt * 8 + 2 * (lane & 3);
+                    if (a.ranges > 1) {
+                        *reinterpret_cast<float2*>(a.partial + (size_t)blockIdx.y * a.n_tokens * HD + at) = make_float2(acc[x][2 * r], acc[x][2 * r + 1]);
+                    } else {
+                        *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<T*>(a.out) + at) = __floats2bfloat162_rn(acc[x][2 * r], acc[x][2 * r + 1]);
+                    }
+                }
+            }
+        }
+    }
+}
+
+// (KC, HG, NT) of the tensor-core kernel for a shape, or false when it does not take it
+static bool mma_plan(int H, int G, int dk, int dv, int page, int* KC_out, int* HG_out, int* NT_out, size_t* smem_out) {
+    if (dk % 16 || dv % 8 || H % G) return false;
+    for (int HG = 1; HG <= H; HG *= 2) {
+        if (H % HG) break;
+        const int own_tiles = (H / HG) * (dv / 8);
+        const int nt = (own_tiles + 7) / 8;
+        if (nt > 16) continue;
+        for (int KC = 32; KC >= 16; KC /= 2) {
+            if (page % KC) continue;
+            const MmaLayout l = mma_layout(H, G, dk, dv, KC, HG);
+            if (l.total <= 220 * 1024) {
+                *KC_out = KC;
+                *HG_out = HG;
+                *NT_out = nt <= 4 ? 4 : (nt <= 8 ? 8 : 16);
+                *smem_out = l.total;
+                return true;
+            }
+        }
+    }
+    return false;
+}
+
 // out[n, :] = the ranges' partial outputs added in order; rows of no sequence get zeros
 template <typename T>
 __global__ void add_ranges_kernel(const float* __restrict__ partial, T* __restrict__ out, const int* __restrict__ token_seq,
@@ -307,6 +541,35 @@ BLM_API int blm_sigmoid_attention_takes(int dtype, int H, int G, int dk, int dv,
     return dtype == BLM_F32 ? plan_for<float>(H, G, dk, dv, 1, page, &p) : plan_for<__nv_bfloat16>(H, G, dk, dv, 1, page, &p);
 }
 
+static int finish_ranges_bf16(const SigmoidAttnArgs& a, const int* token_seq, cudaStream_t stream);
+
+// prompts in bfloat16 whose shape the tensor-core kernel takes; returns -1 when it does not
+static int launch_sigmoid_attention_mma(SigmoidAttnArgs a, int max_q_len, const int* token_seq, cudaStream_t stream) {
+    int KC, HG, NT;
+    size_t smem;
+    if (max_q_len < 8 || !mma_plan(a.H, a.G, a.dk, a.dv, a.page, &KC, &HG, &NT, &smem)) return -1;
+    if ((((size_t)a.q | (size_t)a.pool | (size_t)a.out) & 15) != 0) return -1;
+    a.BQ = kRows;
+    a.KC = KC;
+    a.q_tiles = (max_q_len + kRows - 1) / kRows;
+    BLM_REQUIRE((long long)a.n_seqs * a.q_tiles <= 0x7fffffffLL && a.ranges <= 65535 && HG <= 65535, "sigmoid_attention: grid too large");
+    dim3 grid(a.n_seqs * a.q_tiles, a.ranges, HG);
+#define BLM_SAM(N)                                                                                                       \
+    {                                                                                                                    \
+        auto k = sigmoid_attn_mma_kernel<N>;                                                                             \
+        if (smem > 48 * 1024) {                                                                                          \
+            cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);             \
+            if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "sigmoid_attention: %s", cudaGetErrorString(e));       \
+        }                                                                                                                \
+        k<<<grid, kThreads, smem, stream>>>(a, HG);                                                                      \
+    }
+    if (NT == 4) BLM_SAM(4) else if (NT == 8) BLM_SAM(8) else BLM_SAM(16)
+#undef BLM_SAM
+    int rc = blm_check_launch("sigmoid_attention (tensor cores)");
+    if (rc != BLM_OK || a.ranges == 1) return rc;
+    return finish_ranges_bf16(a, token_seq, stream);
+}
+
 template <typename T>
 static int launch_sigmoid_attention(SigmoidAttnArgs a, int max_q_len, const int* token_seq, cudaStream_t stream) {
     SigmoidAttnPlan p;
@@ -336,11 +599,18 @@ static int launch_sigmoid_attention(SigmoidAttnArgs a, int max_q_len, const int*
     return blm_check_launch("sigmoid_attention (ranges)");
 }
 
+static int finish_ranges_bf16(const SigmoidAttnArgs& a, const int* token_seq, cudaStream_t stream) {
+    const int HD = a.H * a.dv;
+    dim3 grid2((HD + 255) / 256, a.n_tokens);
+    add_ranges_kernel<__nv_bfloat16><<<grid2, 256, 0, stream>>>(a.partial, (__nv_bfloat16*)a.out, token_seq, a.n_tokens, HD, a.ranges);
+    return blm_check_launch("sigmoid_attention (ranges)");
+}
+
 BLM_API int blm_sigmoid_attention(const void* q, const void* pool, int dtype, const int* block_table, int table_stride,
                                   const int* cu_seqlens, const int* slot_of_seq, const int* start_pos, const int* token_seq,
                                   const float* talk, const float* head_bias, void* out, float* partial, int n_tokens, int n_seqs,
                                   int max_q_len, int H, int G, int dk, int dv, int page, int ranges, float scale, float softcap,
-                                  cudaStream_t stream) {
+                                  int scalar_only, cudaStream_t stream) {
     if (n_tokens == 0 || n_seqs == 0) return BLM_OK;
     BLM_REQUIRE(H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0 && max_q_len > 0, "sigmoid_attention: bad sizes");
     BLM_REQUIRE(ranges >= 1 && (ranges == 1 || partial != nullptr), "sigmoid_attention: several key ranges need a workspace");
@@ -351,6 +621,12 @@ BLM_API int blm_sigmoid_attention(const void* q, const void* pool, int dtype, co
     a.n_tokens = n_tokens; a.n_seqs = n_seqs; a.q_tiles = 0; a.H = H; a.G = G; a.dk = dk; a.dv = dv; a.page = page; a.BQ = 0; a.KC = 0;
     a.ranges = ranges; a.scale = scale; a.softcap = softcap;
     if (dtype == BLM_F32) return launch_sigmoid_attention<float>(a, max_q_len, token_seq, stream);
-    if (dtype == BLM_BF16) return launch_sigmoid_attention<__nv_bfloat16>(a, max_q_len, token_seq, stream);
+    if (dtype == BLM_BF16) {
+        if (!scalar_only) {
+            const int rc = launch_sigmoid_attention_mma(a, max_q_len, token_seq, stream);
+            if (rc >= 0) return rc;
+        }
+        return launch_sigmoid_attention<__nv_bfloat16>(a, max_q_len, token_seq, stream);
+    }
     return blm_fail(BLM_BAD_ARGUMENT, "sigmoid_attention: dtype %d", dtype);
 }

@@ -123,7 +123,7 @@ _protos = {
                                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "blm_sigmoid_attention": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                  c_float, c_float, c_void_p],
+                                  c_float, c_float, c_int, c_void_p],
         "blm_sigmoid_attention_takes": [c_int, c_int, c_int, c_int, c_int, c_int],
     },
     "moe": {
@@ -1131,12 +1131,13 @@ def sigmoid_attention_takes(dtype, n_heads, n_kv, key_dim, value_dim) -> bool:
 
 
 def sigmoid_attention(q, pool, block_table, step, out, n_heads, n_kv, key_dim, value_dim, scale, softcap=0.0, talk=None,
-                      head_bias=None, ranges=1, partial=None):
+                      head_bias=None, ranges=1, partial=None, scalar_only=False):
     """Causal attention whose weights are sigmoid(cap(scale q.k) + head_bias) without a normalisation over the keys, mixed
     across heads by talk [heads, heads] (row h: what head h takes of every head's weights) before they meet the values.
     q [N, heads * key_dim] and out [N, heads * value_dim] in the cache's dtype (out must hold zeros in rows of no
     sequence); `ranges` > 1 cuts every query's keys over that many blocks whose partial outputs (`partial`, float32
-    with room for ranges * N * heads * value_dim) are added in order."""
+    with room for ranges * N * heads * value_dim) are added in order.  Prompts in bfloat16 run the tensor-core kernel where
+    it takes the shape (key lanes in multiples of 16, value lanes of 8); `scalar_only` keeps them off it."""
     _need_cuda(q, pool, block_table, out, talk, head_bias, partial)
     _f32(talk, head_bias, partial)
     n = step.n_tokens
@@ -1151,4 +1152,4 @@ def sigmoid_attention(q, pool, block_table, step, out, n_heads, n_kv, key_dim, v
     _call("attention_sigmoid", "blm_sigmoid_attention", _ptr(q), _ptr(pool), _code(pool.dtype), _ptr(block_table), block_table.shape[1],
           _ptr(step.cu_seqlens), _ptr(step.slot_of_seq), _ptr(step.start_pos), _ptr(step.token_seq), _ptr(talk), _ptr(head_bias),
           _ptr(out), _ptr(partial), n, step.n_seqs, step.max_q_len, n_heads, n_kv, key_dim, value_dim, PAGE, int(ranges),
-          c_float(scale), c_float(softcap), _stream(), kernels=2 if ranges > 1 else 1)
+          c_float(scale), c_float(softcap), 1 if scalar_only else 0, _stream(), kernels=2 if ranges > 1 else 1)

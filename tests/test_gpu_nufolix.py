@@ -273,7 +273,7 @@ def test_group_norm_with_its_gate_on_either_side(dtype):
     assert close(out.float().cpu().numpy(), want, tol)
 
 
-def _attend(dtype, H, G, dk, dv, rot, q, k, v, bias, talk, pb, scale, cap, portions, base=10000.0, ranges=1, pages=None):
+def _attend(dtype, H, G, dk, dv, rot, q, k, v, bias, talk, pb, scale, cap, portions, base=10000.0, ranges=1, pages=None, scalar_only=False):
     """q, k, v: projections before bias and rotation, [T, ...] of one sequence, run in the given portions through the append
     kernel and the attention; returns the outputs [T, H * dv]."""
     from burn_lm_b200 import kernels as K
@@ -293,7 +293,7 @@ def _attend(dtype, H, G, dk, dv, rot, q, k, v, bias, talk, pb, scale, cap, porti
         out = torch.zeros((portion, H * dv), dtype=dtype, device="cuda")
         partial = torch.empty(ranges * portion * H * dv, device="cuda") if ranges > 1 else None
         K.sigmoid_attention(qo, pool, table, st, out, H, G, dk, dv, scale, softcap=cap, talk=dev(talk) if talk is not None else None,
-                            head_bias=dev(pb) if pb is not None else None, ranges=ranges, partial=partial)
+                            head_bias=dev(pb) if pb is not None else None, ranges=ranges, partial=partial, scalar_only=scalar_only)
         outs.append(out.float().cpu().numpy())
         at += portion
     return np.concatenate(outs)
@@ -329,8 +329,10 @@ def test_sigmoid_attention_in_prompts_portions_and_single_tokens(dtype, H, G, dk
     tol = 2e-5 if dtype == torch.float32 else 3e-2
     for portions, ranges, pages in (((150,), 1, None), ((63, 1, 1, 2, 70, 5, 1, 1, 1, 1, 1, 1, 1, 1), 1, [4, 0, 2]), ((100, 50), 3, [1, 5, 3]),
                                     ((140,) + (1,) * 10, 2, None)):
-        got = _attend(dtype, H, G, dk, dv, rot, q, k, v, bias, talk, pb, scale, cap, portions, ranges=ranges, pages=pages)
-        assert close(got, want, tol), (portions, ranges)
+        for scalar_only in ((False, True) if dtype == torch.bfloat16 else (False,)):     # prompts on and off the tensor cores
+            got = _attend(dtype, H, G, dk, dv, rot, q, k, v, bias, talk, pb, scale, cap, portions, ranges=ranges, pages=pages,
+                          scalar_only=scalar_only)
+            assert close(got, want, tol), (portions, ranges, scalar_only)
     # without a cap, a mix or the biases
     got = _attend(dtype, H, G, dk, dv, rot, q, k, v, None, None, None, scale, 0.0, (90, 60))
     big = _plain_attention(H, G, dk, dv, rot, q, k, v, None, None, None, scale, 1e9)
