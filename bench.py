@@ -451,7 +451,7 @@ def nufolix_kernels(z, pk):
                                                    ranges=ranges, partial=partial), reps=3)
         return ms_llama, ms_new, total
 
-    ms_l, ms_n, total = attention_case(1, 2048, 0, 1)
+    ms_l, ms_n, total = attention_case(1, 2048, 0, 3)          # the key ranges the mixer takes at this size
     pairs = 2048 * 2049 / 2
     flops = 4.0 * H * hd * pairs
     mix = 2.0 * H * H * pairs                      # the heads' mix: fp32 multiply-adds outside the tensor cores

@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(kThreads) sigmoid_attn_kernel(const SigmoidAtt
     T* Qs = reinterpret_cast<T*>(Ms + H * BQ * KC);                  // [H][BQ][dkp]
     T* KVs = Qs + (size_t)H * BQ * dkp;                              // [G][KC][kvp]
     const int tid = threadIdx.x;
-    const int seq = blockIdx.x / a.q_tiles, tile = blockIdx.x % a.q_tiles;
+    const int seq = blockIdx.x / a.q_tiles, tile = a.q_tiles - 1 - blockIdx.x % a.q_tiles;     // a sequence's last rows, with the most keys, first
     const int first = a.cu_seqlens[seq];
     const int n_new = a.cu_seqlens[seq + 1] - first;
     const int i0 = tile * BQ;
@@ -252,7 +252,7 @@ __global__ void __launch_bounds__(kThreads) sigmoid_attn_kernel(const SigmoidAtt
 }
 
 // ---------------------------------------------------------------------------------------------
-// The same attention on the tensor cores (bfloat16, prompts): 16 query rows of one sequence a block, all heads' scores by
+// The same attention on the tensor cores (bfloat16): 16 query rows of one sequence a block, all heads' scores by
 // mma.sync m16n8k16 (Q rows x a chunk of keys), the weights and their mix in fp32 on the CUDA cores, the mixed weights
 // rounded to bfloat16 for the second product with the values.  Heads are cut into grid.z groups for the second product
 // only (every block needs every head's weights for the mix), so that a block's outputs fit its registers.
@@ -276,6 +276,7 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const unsigned (&a)[4],
 }
 
 constexpr int kRows = 16;          // query rows of a block of the tensor-core kernel
+constexpr int kThreadsMma = 512;   // sixteen warps: the weights' exponentials and the mix want many warps in flight
 
 struct MmaLayout {                 // strides and offsets (bytes) of the block's shared memory
     int dkp, dvp, kvp, ssp, msp, hown, hpad;
@@ -302,7 +303,7 @@ __host__ __device__ inline MmaLayout mma_layout(int H, int G, int dk, int dv, in
 }
 
 template <int NT>      // 16 x 8 output tiles a warp owns
-__global__ void __launch_bounds__(kThreads) sigmoid_attn_mma_kernel(const SigmoidAttnArgs a, int HG) {
+__global__ void __launch_bounds__(kThreadsMma) sigmoid_attn_mma_kernel(const SigmoidAttnArgs a, int HG) {
     typedef __nv_bfloat16 T;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int H = a.H, G = a.G, dk = a.dk, dv = a.dv, KC = a.KC;
@@ -314,7 +315,7 @@ __global__ void __launch_bounds__(kThreads) sigmoid_attn_mma_kernel(const Sigmoi
     T* Qs = reinterpret_cast<T*>(smem_raw + L.qs);
     T* KVs = reinterpret_cast<T*>(smem_raw + L.kv);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int seq = blockIdx.x / a.q_tiles, tile = blockIdx.x % a.q_tiles;
+    const int seq = blockIdx.x / a.q_tiles, tile = a.q_tiles - 1 - blockIdx.x % a.q_tiles;     // a sequence's last rows, with the most keys, first
     const int first = a.cu_seqlens[seq];
     const int n_new = a.cu_seqlens[seq + 1] - first;
     const int i0 = tile * kRows;
@@ -331,15 +332,16 @@ __global__ void __launch_bounds__(kThreads) sigmoid_attn_mma_kernel(const Sigmoi
     const int h0 = blockIdx.z * L.hown;                 // this block's heads for the second product
     const int dv8 = dv / 8;
     const int own_tiles = L.hown * dv8;
+    const int g_lo = h0 / per_kv, g_n = (h0 + L.hown - 1) / per_kv - g_lo + 1;
 
-    for (int e = tid; e < H * L.hpad; e += kThreads) {
+    for (int e = tid; e < H * L.hpad; e += kThreadsMma) {
         const int g = e / L.hpad, hl = e % L.hpad;
         Ts[e] = hl < L.hown ? (a.talk ? a.talk[(size_t)(h0 + hl) * H + g] : (h0 + hl == g ? 1.f : 0.f)) : 0.f;
     }
-    for (int e = tid; e < H; e += kThreads) pbs[e] = a.head_bias ? a.head_bias[e] : 0.f;
+    for (int e = tid; e < H; e += kThreadsMma) pbs[e] = a.head_bias ? a.head_bias[e] : 0.f;
     const T* q = reinterpret_cast<const T*>(a.q);
     const int dk8 = dk / 8;
-    for (int e = tid; e < H * kRows * dk8; e += kThreads) {          // 16-byte pieces of the tile's queries
+    for (int e = tid; e < H * kRows * dk8; e += kThreadsMma) {          // 16-byte pieces of the tile's queries
         const int c = e % dk8, i = (e / dk8) % kRows, h = e / (dk8 * kRows);
         uint4 v = make_uint4(0, 0, 0, 0);
         if (i < nq) v = *reinterpret_cast<const uint4*>(q + (size_t)(first + i0 + i) * H * dk + h * dk + c * 8);
@@ -359,7 +361,7 @@ __global__ void __launch_bounds__(kThreads) sigmoid_attn_mma_kernel(const Sigmoi
         const T* pg = pool + (size_t)table[j0 / a.page] * page_elems;
         const int at0 = j0 % a.page;
         __syncthreads();
-        for (int e = tid; e < G * KC * dk8; e += kThreads) {
+        for (int e = tid; e < G * KC * dk8; e += kThreadsMma) {
             const int c = e % dk8, j = (e / dk8) % KC, g = e / (dk8 * KC);
             uint4 v = make_uint4(0, 0, 0, 0);
             if (j0 + j < kv_hi) v = *reinterpret_cast<const uint4*>(pg + ((size_t)g * a.page + at0 + j) * dk + c * 8);
@@ -367,7 +369,7 @@ __global__ void __launch_bounds__(kThreads) sigmoid_attn_mma_kernel(const Sigmoi
         }
         __syncthreads();
         // scores of all heads on the tensor cores, weights in fp32
-        for (int s = warp; s < n_tiles_s; s += kThreads / 32) {
+        for (int s = warp; s < n_tiles_s; s += kThreadsMma / 32) {
             const int h = s / (KC / 8), nt = s % (KC / 8);
             float c4[4] = {0.f, 0.f, 0.f, 0.f};
             const T* qa = Qs + (size_t)(h * kRows + (lane & 15)) * L.dkp + (lane >> 4) * 8;
@@ -389,8 +391,8 @@ __global__ void __launch_bounds__(kThreads) sigmoid_attn_mma_kernel(const Sigmoi
                     float w = 0.f;
                     if (i < nq && j0 + j <= start + i0 + i) {
                         float sc = c4[2 * r + cc] * a.scale;
-                        if (cap) sc = a.softcap * tanhf(sc * inv_cap);
-                        w = 1.0f / (1.0f + expf(-(sc + pb)));
+                        if (cap) sc = a.softcap * (1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * sc * inv_cap)));     // cap tanh(sc / cap)
+                        w = __fdividef(1.0f, 1.0f + __expf(-(sc + pb)));
                     }
                     w2[cc] = w;
                 }
@@ -399,20 +401,20 @@ __global__ void __launch_bounds__(kThreads) sigmoid_attn_mma_kernel(const Sigmoi
         }
         __syncthreads();
         // the values take the keys' place while the weights of this block's heads are mixed
-        for (int e = tid; e < G * KC * dv8; e += kThreads) {
-            const int c = e % dv8, j = (e / dv8) % KC, g = e / (dv8 * KC);
+        for (int e = tid; e < g_n * KC * dv8; e += kThreadsMma) {          // only the value heads this block's heads read
+            const int c = e % dv8, j = (e / dv8) % KC, g = g_lo + e / (dv8 * KC);
             uint4 v = make_uint4(0, 0, 0, 0);
             if (j0 + j < kv_hi) v = *reinterpret_cast<const uint4*>(pg + (size_t)G * a.page * dk + ((size_t)g * a.page + at0 + j) * dv + c * 8);
             *reinterpret_cast<uint4*>(KVs + (size_t)(g * KC + j) * L.dvp + c * 8) = v;
         }
-        for (int e = tid; e < (L.hpad / 8) * kRows * KC; e += kThreads) {
+        for (int e = tid; e < (L.hpad / 8) * kRows * KC; e += kThreadsMma) {
             const int j = e % KC, i = (e / KC) % kRows, hc = e / (KC * kRows);
             float m[8];
 #pragma unroll
             for (int x = 0; x < 8; ++x) m[x] = 0.f;
             const float* sp = Ss + (size_t)i * L.ssp + j;
             const float* tp = Ts + hc * 8;
-            for (int g = 0; g < H; ++g) {
+            for (int g = 0; g < (i < nq ? H : 0); ++g) {      // rows beyond the tile's queries (single tokens) stay zero
                 const float sv = sp[(size_t)g * kRows * L.ssp];
                 const float4 t0 = *reinterpret_cast<const float4*>(tp + (size_t)g * L.hpad);
                 const float4 t1 = *reinterpret_cast<const float4*>(tp + (size_t)g * L.hpad + 4);
@@ -468,15 +470,16 @@ static bool mma_plan(int H, int G, int dk, int dv, int page, int* KC_out, int* H
     for (int HG = 1; HG <= H; HG *= 2) {
         if (H % HG) break;
         const int own_tiles = (H / HG) * (dv / 8);
-        const int nt = (own_tiles + 7) / 8;
-        if (nt > 16) continue;
+        const int nt = (own_tiles + kThreadsMma / 32 - 1) / (kThreadsMma / 32);
+        if (nt > 8) continue;
         for (int KC = 32; KC >= 16; KC /= 2) {
             if (page % KC) continue;
             const MmaLayout l = mma_layout(H, G, dk, dv, KC, HG);
-            if (l.total <= 220 * 1024) {
+            if (l.total <= 226 * 1024) {      // of the 227 KB a block can have
+
                 *KC_out = KC;
                 *HG_out = HG;
-                *NT_out = nt <= 4 ? 4 : (nt <= 8 ? 8 : 16);
+                *NT_out = nt <= 2 ? 2 : (nt <= 4 ? 4 : 8);
                 *smem_out = l.total;
                 return true;
             }
@@ -543,11 +546,12 @@ BLM_API int blm_sigmoid_attention_takes(int dtype, int H, int G, int dk, int dv,
 
 static int finish_ranges_bf16(const SigmoidAttnArgs& a, const int* token_seq, cudaStream_t stream);
 
-// prompts in bfloat16 whose shape the tensor-core kernel takes; returns -1 when it does not
+// bfloat16 steps whose shape the tensor-core kernel takes (single tokens too: a tile then has one row, which costs the
+// tensor cores nothing that matters beside the keys' and values' way in); returns -1 when it does not
 static int launch_sigmoid_attention_mma(SigmoidAttnArgs a, int max_q_len, const int* token_seq, cudaStream_t stream) {
     int KC, HG, NT;
     size_t smem;
-    if (max_q_len < 8 || !mma_plan(a.H, a.G, a.dk, a.dv, a.page, &KC, &HG, &NT, &smem)) return -1;
+    if (!mma_plan(a.H, a.G, a.dk, a.dv, a.page, &KC, &HG, &NT, &smem)) return -1;
     if ((((size_t)a.q | (size_t)a.pool | (size_t)a.out) & 15) != 0) return -1;
     a.BQ = kRows;
     a.KC = KC;
@@ -561,9 +565,9 @@ static int launch_sigmoid_attention_mma(SigmoidAttnArgs a, int max_q_len, const 
             cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);             \
             if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "sigmoid_attention: %s", cudaGetErrorString(e));       \
         }                                                                                                                \
-        k<<<grid, kThreads, smem, stream>>>(a, HG);                                                                      \
+        k<<<grid, kThreadsMma, smem, stream>>>(a, HG);                                                                     \
     }
-    if (NT == 4) BLM_SAM(4) else if (NT == 8) BLM_SAM(8) else BLM_SAM(16)
+    if (NT == 2) BLM_SAM(2) else if (NT == 4) BLM_SAM(4) else BLM_SAM(8)
 #undef BLM_SAM
     int rc = blm_check_launch("sigmoid_attention (tensor cores)");
     if (rc != BLM_OK || a.ranges == 1) return rc;

@@ -7,17 +7,19 @@
 // what it read, and running it again (a warm-up before a captured graph, a step enqueued ahead and then forgotten)
 // gives the same result.  A step that starts at position 0 reads zeros whatever the block holds.
 //
-// A scan block owns (sequence, head, 32 value columns): 256 threads = 32 columns x 8 row groups; thread (col, rg) keeps
-// rows rg, rg + 8, rg + 16, ... of its column in registers.  A sum over rows is a thread's partial sum and then three
-// shuffles over the eight row groups: the same order whatever the step's size or batch.  The state is stored as
-// [head][row / 8][column][row % 8], which is the order in which a warp holds it.
+// A scan block owns (sequence, head, some value columns): 256 threads = columns x row groups; thread (col, rg) keeps rows
+// rg, rg + RG, rg + 2 RG, ... of its column in registers.  A sum over rows is a thread's partial sum and then shuffles
+// over the row groups (adjacent lanes): the same order whatever the step's size or batch.  RG = 8 (32 columns a block).
+// A warp a column (RG = 32, four times the warps, a quarter of the rows a thread) was measured and is slower: a 2,048-token
+// scan of 64 heads x 128 rows x 64 lanes 0.97 against 0.86 ms, 64 single tokens 0.117 against 0.067 ms: every block stages
+// the same B and C rows for a quarter of the columns.  The state is stored as [head][row / RG][column][row % RG], which is
+// the order in which a warp holds it.
 #include "common.cuh"
 
 BLM_API const char* blm_recurrent_last_error() { return g_blm_error; }
 
 constexpr int kMaxTaps = 8;
-constexpr int kCols = 32;          // value columns a scan block owns
-constexpr int kRowGroups = 8;
+constexpr int kScanThreads = 256;
 constexpr int kChunk = 32;         // tokens staged in shared memory at a time
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
@@ -132,25 +134,25 @@ __device__ __forceinline__ ScanSeq scan_seq(int seq, const int* cu_seqlens, cons
     return s;
 }
 
-__device__ __forceinline__ float group_sum(float v) {       // over the eight row groups of a column (adjacent lanes)
-    v += __shfl_xor_sync(0xffffffffu, v, 1);
-    v += __shfl_xor_sync(0xffffffffu, v, 2);
-    v += __shfl_xor_sync(0xffffffffu, v, 4);
+template <int RG>
+__device__ __forceinline__ float group_sum(float v) {       // over the row groups of a column (adjacent lanes)
+#pragma unroll
+    for (int o = 1; o < RG; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
 
 // State-space scan.  Per head h (group g = h / (heads / groups)), S [N x dv]:
 //     S <- exp(-exp(A_log_h) dt) S + dt B x^T;   y = S^T C + D_h x,    dt = softplus(dt_raw + dt_bias_h)
 // xbc [T, *]: x at x_col0 + h dv, B at b_col0 + g N, C at c_col0 + g N;  dt_raw [T, *] at dt_col0 + h.
-template <int RN>
-__global__ void __launch_bounds__(kCols* kRowGroups)
+template <int RN, int RG>
+__global__ void __launch_bounds__(kScanThreads)
     ssm_scan_kernel(const float* __restrict__ xbc, long long xbc_stride, int x_col0, int b_col0, int c_col0,
                     const float* __restrict__ dt_raw, long long dt_stride, int dt_col0, const float* __restrict__ dt_bias,
                     const float* __restrict__ A_log, const float* __restrict__ D, float* __restrict__ y, long long y_stride,
                     int heads, int groups, int N, int dv, const int* __restrict__ cu_seqlens, const int* __restrict__ slot_of_seq,
                     const int* __restrict__ start_pos, float* __restrict__ state, long long slot_stride, long long copy_stride,
                     long long state_off) {
-    constexpr int NP = RN * kRowGroups;
+    constexpr int NP = RN * RG, kCols = kScanThreads / RG, kRowGroups = RG;
     extern __shared__ float sm[];
     float* Bs = sm;                         // [kChunk][NP]
     float* Cs = Bs + kChunk * NP;           // [kChunk][NP]
@@ -199,7 +201,7 @@ __global__ void __launch_bounds__(kCols* kRowGroups)
                 s[r] = dec * s[r] + (dt * b[r * kRowGroups]) * xv;
                 acc += s[r] * c[r * kRowGroups];
             }
-            acc = group_sum(acc);
+            acc = group_sum<RG>(acc);
             if (rg == 0 && live) y[(size_t)(sq.first + c0 + t) * y_stride + h * dv + col0 + col] = acc + skip * xv;
         }
     }
@@ -213,8 +215,8 @@ __global__ void __launch_bounds__(kCols* kRowGroups)
 //     S <- g[:, None] S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
 // with k, q made unit vectors (x / sqrt(sum x^2 + 1e-6)), q also times dk^(-1/2), beta = sigmoid(b_raw),
 // g = exp(-exp(A_log_h) softplus(a_raw + dt_bias)) per head and key channel.
-template <int RN>
-__global__ void __launch_bounds__(kCols* kRowGroups)
+template <int RN, int RG>
+__global__ void __launch_bounds__(kScanThreads)
     delta_scan_kernel(const float* __restrict__ q, long long q_stride, int q_col0, const float* __restrict__ k, long long k_stride,
                       int k_col0, const float* __restrict__ v, long long v_stride, int v_col0, const float* __restrict__ b_raw,
                       long long b_stride, int b_col0, const float* __restrict__ a_raw, long long a_stride, int a_col0,
@@ -222,7 +224,7 @@ __global__ void __launch_bounds__(kCols* kRowGroups)
                       int heads, int qk_heads, int dk, int dv, const int* __restrict__ cu_seqlens,
                       const int* __restrict__ slot_of_seq, const int* __restrict__ start_pos, float* __restrict__ state,
                       long long slot_stride, long long copy_stride, long long state_off) {
-    constexpr int NP = RN * kRowGroups;
+    constexpr int NP = RN * RG, kCols = kScanThreads / RG, kRowGroups = RG;
     extern __shared__ float sm[];
     float* ks = sm;                          // [kChunk][NP]
     float* qs = ks + kChunk * NP;            // [kChunk][NP]
@@ -286,7 +288,7 @@ __global__ void __launch_bounds__(kCols* kRowGroups)
                 s[r] *= gg[r * kRowGroups];
                 acc += s[r] * kk[r * kRowGroups];
             }
-            acc = group_sum(acc);
+            acc = group_sum<RG>(acc);
             const float u = beta * (vv - acc);
             float out = 0.f;
 #pragma unroll
@@ -294,7 +296,7 @@ __global__ void __launch_bounds__(kCols* kRowGroups)
                 s[r] += kk[r * kRowGroups] * u;
                 out += s[r] * qq[r * kRowGroups];
             }
-            out = group_sum(out);
+            out = group_sum<RG>(out);
             if (rg == 0 && live) o[(size_t)(sq.first + c0 + t) * o_stride + h * dv + col0 + col] = out;
         }
     }
@@ -304,16 +306,11 @@ __global__ void __launch_bounds__(kCols* kRowGroups)
     }
 }
 
-static int rows_per_thread(int n) {       // the smallest instance that holds n rows: 8 row groups x RN
+static int row_groups(int) { return 8; }
+static int rows_per_thread(int n) {       // the smallest instance that holds n rows: row groups x RN
     for (int rn : {1, 2, 4, 8, 16, 32})
-        if (rn * kRowGroups >= n) return rn;
+        if (rn * row_groups(n) >= n) return rn;
     return 0;
-}
-
-// floats of one copy of a scan's state: heads x (rows rounded up to its instance) x dv
-BLM_API long long blm_scan_state_floats(int heads, int rows, int dv) {
-    const int rn = rows_per_thread(rows);
-    return rn ? (long long)heads * rn * kRowGroups * dv : -1;
 }
 
 template <typename Kern>
@@ -332,24 +329,20 @@ BLM_API int blm_ssm_scan(const float* xbc, long long xbc_stride, int x_col0, int
                          long long state_off, cudaStream_t stream) {
     if (n_seqs == 0) return BLM_OK;
     const int rn = rows_per_thread(N);
-    BLM_REQUIRE(rn > 0, "ssm_scan: a state of %d rows; this kernel takes up to %d", N, 32 * kRowGroups);
+    BLM_REQUIRE(rn > 0, "ssm_scan: a state of %d rows; this kernel takes up to %d", N, 32 * 8);
     BLM_REQUIRE(heads > 0 && groups > 0 && heads % groups == 0 && dv > 0, "ssm_scan: bad head counts");
-    BLM_REQUIRE(heads <= 65535 && (dv + kCols - 1) / kCols <= 65535, "ssm_scan: too many heads");
-    dim3 grid(n_seqs, heads, (dv + kCols - 1) / kCols);
-    const size_t smem = ((size_t)2 * kChunk * rn * kRowGroups + kChunk * kCols + 2 * kChunk) * sizeof(float);
-#define BLM_SSM(RN)                                                                                                          \
-    case RN: {                                                                                                               \
-        int rc = allow_smem(ssm_scan_kernel<RN>, smem, "ssm_scan");                                                          \
-        if (rc != BLM_OK) return rc;                                                                                         \
-        ssm_scan_kernel<RN><<<grid, kCols * kRowGroups, smem, stream>>>(xbc, xbc_stride, x_col0, b_col0, c_col0, dt_raw,     \
-            dt_stride, dt_col0, dt_bias, A_log, D, y, y_stride, heads, groups, N, dv, cu_seqlens, slot_of_seq, start_pos,    \
-            state, slot_stride, copy_stride, state_off);                                                                     \
-        break;                                                                                                               \
+    BLM_REQUIRE(heads <= 65535 && dv <= 65535 * 8, "ssm_scan: too many heads");
+    const int rg = row_groups(N), cols = kScanThreads / rg;
+    dim3 grid(n_seqs, heads, (dv + cols - 1) / cols);
+    const size_t smem = ((size_t)2 * kChunk * rn * rg + kChunk * cols + 2 * kChunk) * sizeof(float);
+#define BLM_SCAN(RN, RG)                                                                                 \
+    if (rn == RN && rg == RG) {                                                                          \
+        int rc = allow_smem(ssm_scan_kernel<RN, RG>, smem, "ssm_scan_kernel");                                   \
+        if (rc != BLM_OK) return rc;                                                                     \
+        ssm_scan_kernel<RN, RG><<<grid, kScanThreads, smem, stream>>>(xbc, xbc_stride, x_col0, b_col0, c_col0, dt_raw, dt_stride, dt_col0, dt_bias, A_log, D, y, y_stride, heads, groups, N, dv, cu_seqlens, slot_of_seq, start_pos, state, slot_stride, copy_stride, state_off); \
     }
-    switch (rn) {
-        BLM_SSM(1) BLM_SSM(2) BLM_SSM(4) BLM_SSM(8) BLM_SSM(16) BLM_SSM(32)
-    }
-#undef BLM_SSM
+    BLM_SCAN(1, 8) BLM_SCAN(2, 8) BLM_SCAN(4, 8) BLM_SCAN(8, 8) BLM_SCAN(16, 8) BLM_SCAN(32, 8)
+#undef BLM_SCAN
     return blm_check_launch("ssm_scan");
 }
 
@@ -361,24 +354,20 @@ BLM_API int blm_delta_scan(const float* q, long long q_stride, int q_col0, const
                            long long copy_stride, long long state_off, cudaStream_t stream) {
     if (n_seqs == 0) return BLM_OK;
     const int rn = rows_per_thread(dk);
-    BLM_REQUIRE(rn > 0, "delta_scan: keys of %d lanes; this kernel takes up to %d", dk, 32 * kRowGroups);
+    BLM_REQUIRE(rn > 0, "delta_scan: keys of %d lanes; this kernel takes up to %d", dk, 32 * 8);
     BLM_REQUIRE(heads > 0 && qk_heads > 0 && heads % qk_heads == 0 && dv > 0, "delta_scan: bad head counts");
-    BLM_REQUIRE(heads <= 65535 && (dv + kCols - 1) / kCols <= 65535, "delta_scan: too many heads");
-    dim3 grid(n_seqs, heads, (dv + kCols - 1) / kCols);
-    const size_t smem = ((size_t)3 * kChunk * rn * kRowGroups + kChunk * kCols + kChunk) * sizeof(float);
-#define BLM_DELTA(RN)                                                                                                        \
-    case RN: {                                                                                                               \
-        int rc = allow_smem(delta_scan_kernel<RN>, smem, "delta_scan");                                                      \
-        if (rc != BLM_OK) return rc;                                                                                         \
-        delta_scan_kernel<RN><<<grid, kCols * kRowGroups, smem, stream>>>(q, q_stride, q_col0, k, k_stride, k_col0, v,       \
-            v_stride, v_col0, b_raw, b_stride, b_col0, a_raw, a_stride, a_col0, dt_bias, A_log, o, o_stride, heads,          \
-            qk_heads, dk, dv, cu_seqlens, slot_of_seq, start_pos, state, slot_stride, copy_stride, state_off);               \
-        break;                                                                                                               \
+    BLM_REQUIRE(heads <= 65535 && dv <= 65535 * 8, "delta_scan: too many heads");
+    const int rg = row_groups(dk), cols = kScanThreads / rg;
+    dim3 grid(n_seqs, heads, (dv + cols - 1) / cols);
+    const size_t smem = ((size_t)3 * kChunk * rn * rg + kChunk * cols + 2 * kChunk) * sizeof(float);
+#define BLM_SCAN(RN, RG)                                                                                 \
+    if (rn == RN && rg == RG) {                                                                          \
+        int rc = allow_smem(delta_scan_kernel<RN, RG>, smem, "delta_scan_kernel");                                   \
+        if (rc != BLM_OK) return rc;                                                                     \
+        delta_scan_kernel<RN, RG><<<grid, kScanThreads, smem, stream>>>(q, q_stride, q_col0, k, k_stride, k_col0, v, v_stride, v_col0, b_raw, b_stride, b_col0, a_raw, a_stride, a_col0, dt_bias, A_log, o, o_stride, heads, qk_heads, dk, dv, cu_seqlens, slot_of_seq, start_pos, state, slot_stride, copy_stride, state_off); \
     }
-    switch (rn) {
-        BLM_DELTA(1) BLM_DELTA(2) BLM_DELTA(4) BLM_DELTA(8) BLM_DELTA(16) BLM_DELTA(32)
-    }
-#undef BLM_DELTA
+    BLM_SCAN(1, 8) BLM_SCAN(2, 8) BLM_SCAN(4, 8) BLM_SCAN(8, 8) BLM_SCAN(16, 8) BLM_SCAN(32, 8)
+#undef BLM_SCAN
     return blm_check_launch("delta_scan");
 }
 

@@ -1004,15 +1004,14 @@ def weighted_sum(a, scale_a, b, scale_b, out):
 # ------------------------------------------------------------------------------------------------
 # recurrent mixers
 # ------------------------------------------------------------------------------------------------
-SCAN_ROW_GROUPS = 8
-
-
 def scan_state_floats(heads: int, rows: int, value_dim: int) -> int:
-    """Floats of one copy of a scan's state: the rows are rounded up to what the kernel's instance holds."""
+    """Floats of one copy of a scan's state: the rows are rounded up to what the kernel's instance holds (8 row groups
+    times 1, 2, 4, 8, 16 or 32 rows a thread)."""
+    groups = 8
     for rn in (1, 2, 4, 8, 16, 32):
-        if rn * SCAN_ROW_GROUPS >= rows:
-            return heads * rn * SCAN_ROW_GROUPS * value_dim
-    raise KernelError(f"a recurrent state of {rows} rows: the scan kernels take up to {32 * SCAN_ROW_GROUPS}")
+        if rn * groups >= rows:
+            return heads * rn * groups * value_dim
+    raise KernelError(f"a recurrent state of {rows} rows: the scan kernels take up to 256")
 
 
 def _state_args(state, offset):

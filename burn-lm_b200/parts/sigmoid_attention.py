@@ -94,7 +94,7 @@ class SigmoidAttention(Part):
     def _ranges(self, step) -> int:
         """Over how many blocks a query's keys are cut: nothing is normalised over the keys, so partial outputs just add.
         Few query rows with long pasts (decoding) would leave most multiprocessors idle otherwise."""
-        tiles = step.n_seqs * ((step.max_q_len + 7) // 8)
+        tiles = step.n_seqs * ((step.max_q_len + 15) // 16)
         want = BLOCKS_PER_SM * K.sm_count(self.runtime.device)
         return max(1, min((want + tiles - 1) // tiles, step.max_kv_len // RANGE_KEYS, 64))
 
