@@ -36,7 +36,8 @@ __global__ void conv_kernel(const float* __restrict__ x, long long x_stride, int
                             float* __restrict__ out, long long out_stride, int out_col0,
                             const int* __restrict__ token_seq, const int* __restrict__ cu_seqlens,
                             const int* __restrict__ slot_of_seq, const int* __restrict__ start_pos,
-                            const float* __restrict__ state, long long slot_stride, long long copy_stride, long long hist_off) {
+                            float* __restrict__ state, long long slot_stride, long long copy_stride, long long hist_off,
+                            int carry_here) {
     const int n = blockIdx.y;
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= channels) return;
@@ -48,7 +49,8 @@ __global__ void conv_kernel(const float* __restrict__ x, long long x_stride, int
     }
     const int i = n - cu_seqlens[seq];
     const int start = start_pos[seq];
-    const float* hist = state + (size_t)slot_of_seq[seq] * slot_stride + (size_t)(start & 1) * copy_stride + hist_off;
+    float* both = state + (size_t)slot_of_seq[seq] * slot_stride + hist_off;
+    const float* hist = both + (size_t)(start & 1) * copy_stride;
     float acc = bias ? bias[c] : 0.f;
     for (int j = K - 1; j >= 0; --j) {          // the oldest input first
         const int back = i - j;                   // index among the step's rows of this sequence
@@ -59,6 +61,13 @@ __global__ void conv_kernel(const float* __restrict__ x, long long x_stride, int
         acc += taps[(size_t)c * K + (K - 1 - j)] * v;
     }
     *o = act ? silu_f(acc) : acc;
+    if (carry_here) {        // every sequence brings one token: its thread also moves the carried inputs on, into the other copy
+        float* fresh = both + (size_t)((start + 1) & 1) * copy_stride;
+        for (int m = 0; m < K - 1; ++m) {
+            const int p = start + 1 - (K - 1) + m;          // the position whose input goes to place m
+            fresh[(size_t)m * channels + c] = p < 0 ? 0.f : (p == start ? x[(size_t)n * x_stride + x_col0 + c] : hist[(size_t)(m + 1) * channels + c]);
+        }
+    }
 }
 
 __global__ void conv_carry_kernel(const float* __restrict__ x, long long x_stride, int x_col0, int channels, int K,
@@ -96,7 +105,7 @@ BLM_API int blm_causal_conv(const float* x, long long x_stride, int x_col0, int 
                             int K, int act, float* out, long long out_stride, int out_col0, const int* token_seq,
                             const int* cu_seqlens, const int* slot_of_seq, const int* start_pos, int n_tokens, int n_seqs,
                             float* state, long long slot_stride, long long copy_stride, long long hist_off,
-                            cudaStream_t stream) {
+                            int single_tokens, cudaStream_t stream) {
     if (n_tokens == 0) return BLM_OK;
     BLM_REQUIRE(channels > 0 && K >= 1 && K <= kMaxTaps, "causal_conv: %d taps; this kernel takes 1 to %d", K, kMaxTaps);
     BLM_REQUIRE(n_tokens <= 65535 * 64 && n_seqs <= 65535, "causal_conv: too many rows");
@@ -104,9 +113,9 @@ BLM_API int blm_causal_conv(const float* x, long long x_stride, int x_col0, int 
     dim3 grid((channels + threads - 1) / threads, n_tokens);
     conv_kernel<<<grid, threads, 0, stream>>>(x, x_stride, x_col0, channels, taps, bias, K, act, out, out_stride, out_col0,
                                               token_seq, cu_seqlens, slot_of_seq, start_pos, state, slot_stride, copy_stride,
-                                              hist_off);
+                                              hist_off, single_tokens && K > 1 ? 1 : 0);
     int rc = blm_check_launch("causal_conv");
-    if (rc != BLM_OK || K == 1) return rc;
+    if (rc != BLM_OK || K == 1 || single_tokens) return rc;
     dim3 grid2((channels + threads - 1) / threads, n_seqs);
     conv_carry_kernel<<<grid2, threads, 0, stream>>>(x, x_stride, x_col0, channels, K, cu_seqlens, slot_of_seq, start_pos, state,
                                                      slot_stride, copy_stride, hist_off);

@@ -34,13 +34,15 @@ BLM_API int blm_embed_scaled(const int* tokens, const void* table, int table_dty
 }
 
 // ---------------------------------------------------------------------------------------------
-// The sandwich step.  With d = delta (+ bias), a sublayer's raw output:
+// The sandwich step.  With d = delta (+ bias), a sublayer's raw output, or d = sa delta + sb delta2 (+ bias) for two
+// mixers that ran side by side:
 //     h   = resid + mult * (d / sqrt(mean(d^2) + eps_post) * post_w)          (stored unless `rows`)
 //     out = h / sqrt(mean(h^2) + eps_pre) * pre_w                             (when pre_w is given)
 // delta null: h = resid.  rows given: row b of `out` comes from row rows[b]; the stream is left alone.
 // ---------------------------------------------------------------------------------------------
 template <typename TD, typename TA>
-__global__ void sandwich_norm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, const float* __restrict__ bias,
+__global__ void sandwich_norm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, const TD* __restrict__ delta2,
+                                     float sa, float sb, const float* __restrict__ bias,
                                      const float* __restrict__ post_w, const float* __restrict__ pre_w, float mult,
                                      float eps_post, float eps_pre, TA* __restrict__ out, const int* __restrict__ rows,
                                      int width) {
@@ -51,9 +53,11 @@ __global__ void sandwich_norm_kernel(float* __restrict__ resid, const TD* __rest
     float inv_d = 0.f;
     if (delta) {
         const TD* dl = delta + (size_t)src * width;
+        const TD* dl2 = delta2 ? delta2 + (size_t)src * width : nullptr;
         float ss = 0.f;
         for (int d = threadIdx.x; d < width; d += blockDim.x) {
             float v = to_f32(dl[d]);
+            if (dl2) v = sa * v + sb * to_f32(dl2[d]);
             if (bias) v += bias[d];
             row_buf[d] = v;
             ss += v * v;
@@ -79,7 +83,7 @@ __global__ void sandwich_norm_kernel(float* __restrict__ resid, const TD* __rest
 }
 
 template <typename TD, typename TA>
-static int launch_sandwich(float* resid, const void* delta, const float* bias, const float* post_w, const float* pre_w, float mult,
+static int launch_sandwich(float* resid, const void* delta, const void* delta2, float sa, float sb, const float* bias, const float* post_w, const float* pre_w, float mult,
                            float eps_post, float eps_pre, void* out, const int* rows, int n_rows, int width, cudaStream_t stream) {
     const size_t smem = (size_t)(width + 33) * sizeof(float);
     BLM_REQUIRE(smem <= 200 * 1024, "sandwich norm: width %d is beyond what this kernel holds in shared memory", width);
@@ -89,17 +93,19 @@ static int launch_sandwich(float* resid, const void* delta, const float* bias, c
         if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "sandwich norm: %s", cudaGetErrorString(e));
     }
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-    k<<<n_rows, threads, smem, stream>>>(resid, (const TD*)delta, bias, post_w, pre_w, mult, eps_post, eps_pre, (TA*)out, rows, width);
+    k<<<n_rows, threads, smem, stream>>>(resid, (const TD*)delta, (const TD*)delta2, sa, sb, bias, post_w, pre_w, mult, eps_post, eps_pre, (TA*)out, rows, width);
     return blm_check_launch("sandwich_norm");
 }
 
-BLM_API int blm_sandwich_norm(float* resid, const void* delta, int delta_dtype, const float* bias, const float* post_w,
+BLM_API int blm_sandwich_norm(float* resid, const void* delta, const void* delta2, float sa, float sb, int delta_dtype,
+                              const float* bias, const float* post_w,
                               const float* pre_w, float mult, float eps_post, float eps_pre, void* out, int out_dtype,
                               const int* rows, int n_rows, int width, cudaStream_t stream) {
     if (n_rows == 0) return BLM_OK;
     BLM_REQUIRE(n_rows > 0 && width > 0, "sandwich norm: bad sizes");
     BLM_REQUIRE(delta == nullptr || post_w != nullptr, "sandwich norm: an output to add needs its norm's weight");
-#define BLM_SW(TD, TA) return launch_sandwich<TD, TA>(resid, delta, bias, post_w, pre_w, mult, eps_post, eps_pre, out, rows, n_rows, width, stream)
+    BLM_REQUIRE(delta2 == nullptr || delta != nullptr, "sandwich norm: a second output without a first");
+#define BLM_SW(TD, TA) return launch_sandwich<TD, TA>(resid, delta, delta2, sa, sb, bias, post_w, pre_w, mult, eps_post, eps_pre, out, rows, n_rows, width, stream)
     if (delta_dtype == BLM_F32 && out_dtype == BLM_F32) BLM_SW(float, float);
     if (delta_dtype == BLM_F32 && out_dtype == BLM_BF16) BLM_SW(float, __nv_bfloat16);
     if (delta_dtype == BLM_BF16 && out_dtype == BLM_F32) BLM_SW(__nv_bfloat16, float);

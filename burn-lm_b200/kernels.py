@@ -99,15 +99,15 @@ _protos = {
     },
     "stream_ops": {
         "blm_embed_scaled": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
-        "blm_sandwich_norm": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_float, c_float, c_void_p, c_int,
-                              c_void_p, c_int, c_int, c_void_p],
+        "blm_sandwich_norm": [c_void_p, c_void_p, c_void_p, c_float, c_float, c_int, c_void_p, c_void_p, c_void_p, c_float, c_float,
+                              c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
         "blm_bias_act": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "blm_weighted_sum": [c_void_p, c_void_p, c_void_p, c_float, c_float, c_size_t, c_void_p],
     },
     "recurrent": {
         "blm_causal_conv": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_longlong, c_int,
                             c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_longlong, c_longlong, c_longlong,
-                            c_void_p],
+                            c_int, c_void_p],
         "blm_ssm_scan": [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p,
                          c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                          c_longlong, c_longlong, c_longlong, c_void_p],
@@ -952,8 +952,10 @@ def embed_scaled(tokens, table, out, scale: float):
     _call("stream_ops", "blm_embed_scaled", _ptr(tokens), _ptr(table), _code(table.dtype), _ptr(out), n, d, v, c_float(scale), _stream())
 
 
-def sandwich_norm(resid, delta, post_weight, mult, eps_post, pre_weight, eps_pre, out, rows=None, delta_bias=None):
-    """The add of a normed sublayer output fused with the norm that reads the stream next, in fp32.  With d = delta (+ delta_bias):
+def sandwich_norm(resid, delta, post_weight, mult, eps_post, pre_weight, eps_pre, out, rows=None, delta_bias=None, second=None):
+    """The add of a normed sublayer output fused with the norm that reads the stream next, in fp32.  With d = delta (+ delta_bias),
+    or d = scale_a * delta + scale_b * delta_b (+ delta_bias) when `second` = (scale_a, delta_b, scale_b) names the output of
+    a mixer that ran beside the first:
 
         h   = resid + mult * (d / sqrt(mean(d^2) + eps_post) * post_weight)       stored into resid (rows is None)
         out = h / sqrt(mean(h^2) + eps_pre) * pre_weight                          when pre_weight and out are given
@@ -970,7 +972,12 @@ def sandwich_norm(resid, delta, post_weight, mult, eps_post, pre_weight, eps_pre
         raise KernelError("sandwich_norm: out [rows, D] needs the weight [D] of the norm that produces it")
     if rows is not None and rows.dtype != torch.int32:
         raise KernelError("sandwich_norm: rows must be int32")
-    _call("stream_ops", "blm_sandwich_norm", _ptr(resid), _ptr(delta), _code(delta.dtype) if delta is not None else F32,
+    sa, delta_b, sb = second if second is not None else (1.0, None, 0.0)
+    _need_cuda(delta_b)
+    if delta_b is not None and (delta is None or delta_b.shape != delta.shape or delta_b.dtype != delta.dtype):
+        raise KernelError("sandwich_norm: the second output must match the first in shape and dtype")
+    _call("stream_ops", "blm_sandwich_norm", _ptr(resid), _ptr(delta), _ptr(delta_b), c_float(sa), c_float(sb),
+          _code(delta.dtype) if delta is not None else F32,
           _ptr(delta_bias), _ptr(post_weight), _ptr(pre_weight if out is not None else None), c_float(mult), c_float(eps_post),
           c_float(eps_pre), _ptr(out), _code(out.dtype) if out is not None else F32, _ptr(rows), n_out, d, _stream())
 
@@ -1030,7 +1037,8 @@ def _cols(t, col0, width):
 def causal_conv(x, x_col0, channels, taps, bias, out, out_col0, step, state, state_offset, silu=True):
     """y_t = sum_k taps[:, k] x_(t - (K-1) + k) (+ bias) per channel over each sequence's time, then silu; zeros before a
     sequence's start.  x, out float32 [N, *] (the channels at x_col0 / out_col0); taps float32 [C, K]; the last K - 1
-    inputs of every sequence are carried in `state` (float32 [slots, 2, floats]) at state_offset, [K - 1, C]."""
+    inputs of every sequence are carried in `state` (float32 [slots, 2, floats]) at state_offset, [K - 1, C].  A step in
+    which every sequence brings one token (step.max_q_len == 1) moves the carried inputs on in the same launch."""
     _need_cuda(taps, bias, state)
     _f32(taps, bias)
     k = taps.shape[1]
@@ -1040,9 +1048,10 @@ def causal_conv(x, x_col0, channels, taps, bias, out, out_col0, step, state, sta
     op, os_, oc = _cols(out, out_col0, channels)
     if x.shape[0] != step.n_tokens or out.shape[0] != step.n_tokens:
         raise KernelError("causal_conv: a row per token of the step")
+    single = getattr(step, "max_q_len", 0) == 1
     _call("recurrent", "blm_causal_conv", xp, xs, xc, channels, _ptr(taps), _ptr(bias), k, 1 if silu else 0, op, os_, oc,
           _ptr(step.token_seq), _ptr(step.cu_seqlens), _ptr(step.slot_of_seq), _ptr(step.start_pos), step.n_tokens, step.n_seqs,
-          *_state_args(state, state_offset), _stream(), kernels=2 if k > 1 else 1)
+          *_state_args(state, state_offset), 1 if single else 0, _stream(), kernels=2 if k > 1 and not single else 1)
 
 
 def ssm_scan(xbc, x_col0, b_col0, c_col0, dt, dt_col0, dt_bias, a_log, d_skip, y, heads, groups, n_state, value_dim, step, state,

@@ -129,16 +129,22 @@ class SandwichBlock:
 
     @staticmethod
     def _pending(post, result):
-        """A sublayer returns its output, or (output, bias) when its last product's bias is still to be added."""
+        """A sublayer returns its output; or (output, bias) when its last product's bias is still to be added; or a
+        parts.parallel_mixers.WeightedPair when it is a weighted sum of two outputs that is still to be taken."""
         if isinstance(result, tuple):
             return post.pending(result[0], result[1])
+        if hasattr(result, "scale_a"):
+            return post.pending(result.a, second=(result.scale_a, result.b, result.scale_b))
         return post.pending(result)
 
     def forward(self, resid, delta, step, cache_view, next_norm=None):
         if getattr(step, "handoff", None) is not None:
             step.handoff.expect(None)          # no product of this block prepares a norm's input
         h = self.mixer_norm.add_norm(resid, delta)
-        pending = self._pending(self.mixer_post, self.mixer.forward(h, step, cache_view))
+        if getattr(self.mixer, "gives_pairs", False):      # two mixers side by side: the norm's kernel takes their weighted sum
+            pending = self._pending(self.mixer_post, self.mixer.forward(h, step, cache_view, as_pair=True))
+        else:
+            pending = self._pending(self.mixer_post, self.mixer.forward(h, step, cache_view))
         if self.ff is not None:
             h = self.ff_norm.add_norm(resid, pending)
             pending = self._pending(self.ff_post, self.ff.forward(h, step))

@@ -35,6 +35,8 @@ class PostNormed:
     eps: float
     mult: float
     bias: Optional[torch.Tensor] = None     # float32 [D]: a bias of the sublayer's last product, not added yet
+    second: Optional[tuple] = None          # (scale_a, output_b, scale_b): the sublayer's output is scale_a * output +
+                                            # scale_b * output_b (two mixers side by side), summed by the same kernel
 
 
 @register_part("norm", "rmsnorm")
@@ -64,7 +66,7 @@ class RMSNorm(Part):
             if getattr(self, "_gamma32", None) is None:
                 self._gamma32 = self.gamma.to(torch.float32).contiguous()
             K.sandwich_norm(resid, delta.output, delta.weight, delta.mult, delta.eps, self._gamma32, self.spec.eps, out,
-                            rows=rows, delta_bias=delta.bias)
+                            rows=rows, delta_bias=delta.bias, second=delta.second)
             return out
         handed = handoff.claim(resid, self.gamma) if handoff is not None else None
         if lazy and delta is None:
@@ -97,13 +99,14 @@ class PostRMSNorm(Part):
     def bind(self, loaded):
         self.weight = loaded[self.tensor_names["weight"]].to(torch.float32).contiguous()
 
-    def pending(self, output, bias=None) -> PostNormed:
-        return PostNormed(output, self.weight, self.spec.eps, self.spec.mult, bias)
+    def pending(self, output, bias=None, second=None) -> PostNormed:
+        return PostNormed(output, self.weight, self.spec.eps, self.spec.mult, bias, second)
 
     @staticmethod
     def add(resid, pending: PostNormed) -> None:
         """Only the add into the stream (no norm reads it next)."""
-        K.sandwich_norm(resid, pending.output, pending.weight, pending.mult, pending.eps, None, 0.0, None, delta_bias=pending.bias)
+        K.sandwich_norm(resid, pending.output, pending.weight, pending.mult, pending.eps, None, 0.0, None, delta_bias=pending.bias,
+                        second=pending.second)
 
 
 @dataclass(frozen=True)

@@ -24,10 +24,20 @@ class ParallelMixersSpec:
     right_scale: float = 1.0
 
 
+@dataclass
+class WeightedPair:
+    """scale_a * a + scale_b * b, not summed yet: a block whose next kernel can take the sum (`sums_pairs`) gets this."""
+    a: torch.Tensor
+    scale_a: float
+    b: torch.Tensor
+    scale_b: float
+
+
 @register_part("mixer", "parallel_mixers")
 class ParallelMixers(Part):
     family = "mixer"
     roles = ()
+    gives_pairs = True            # forward(..., as_pair=True) leaves the weighted sum to the caller's next kernel
 
     def __init__(self, spec, tensors, runtime):
         super().__init__(spec, tensors, runtime)
@@ -56,11 +66,14 @@ class ParallelMixers(Part):
             needs.extend(need if isinstance(need, tuple) else [need])
         return tuple(n for n in needs if n.kind != "none")
 
-    def forward(self, x, step, cache):
+    def forward(self, x, step, cache, as_pair=False):
+        """`as_pair`: the caller's next kernel takes the weighted sum itself; it gets a WeightedPair."""
         a = self.left.forward(x, step, cache)
         b = self.right.forward(x, step, cache)
         if a.dtype != torch.float32 or b.dtype != torch.float32:
             raise ValueError("mixers that run side by side hand their outputs over in float32")
+        if as_pair:
+            return WeightedPair(a, self.spec.left_scale, b, self.spec.right_scale)
         out = torch.empty_like(a)
         K.weighted_sum(a, self.spec.left_scale, b, self.spec.right_scale, out)
         return out

@@ -101,6 +101,12 @@ def test_the_norm_behind_a_sublayer_and_the_next_norm_in_one_kernel(dtype):
     only = dev(x)
     K.sandwich_norm(only, dev(a), dev(wb), mult, eps, None, 0.0, None)
     assert close(only.cpu().numpy(), x + mult * P.rms_norm(a, wb, eps), 1e-5)
+    # two outputs side by side: their weighted sum is taken first
+    b2 = rng.normal(size=(n, d)) * 5
+    resid = dev(x)
+    K.sandwich_norm(resid, dev(a), dev(wb), mult, eps, dev(w), eps, plain, second=(0.6, dev(b2), -1.3), delta_bias=dev(bias))
+    stream = x + mult * P.rms_norm(0.6 * a + -1.3 * b2 + bias, wb, eps)
+    assert close(resid.cpu().numpy(), stream, 1e-5) and close(plain.float().cpu().numpy(), P.rms_norm(stream, w, eps), tol)
 
 
 def test_xielu_with_a_bias():
@@ -534,3 +540,29 @@ def test_the_trace_runner_as_a_child_process(tmp_path):
         for t in range(4):
             rows = [wa[71 + t]] + ([wb[6 + t]] if t < 3 else [])
             assert row_error(read(2 + t), np.stack(rows)).max() < tol, t
+
+
+def test_the_command_line_on_the_preset(tmp_path):
+    program = [sys.executable, os.path.join(ROOT, "bin", "burn-lm")]
+    folder = str(tmp_path / "n")
+    r = subprocess.run(program + ["random", folder, "--preset", "nufolix_tiny", "--seed", "4", "--dtype", "float32"],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and f"wrote {folder}" in r.stdout, r.stderr
+    cfg, tensors = P.read_model_folder(folder)
+    prompt = random_tokens(5, 23, cfg["vocab"])
+    want = P.greedy(cfg, tensors, prompt, 12)
+    r = subprocess.run(program + ["run", folder, "--dtype", "float32", "--sample-len", "12", "--max-seq-len", "128",
+                                  ",".join(map(str, prompt))], capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr
+    lines = [ln for ln in r.stdout.splitlines() if ln.strip()]
+    assert lines[0].split() == [str(t) for t in want], (lines[0], want)
+
+
+def test_sampling_with_a_temperature_runs_inside_the_captured_step(tmp_path):
+    import burn_lm_b200 as blm
+    folder = make_folder(tmp_path, "nuf_a")
+    lm = blm.load(folder, dtype="bfloat16", max_seq_len=256, max_batch=2)
+    prompts = [random_tokens(50, 20, 320), random_tokens(51, 66, 320)]
+    a = lm.generate(prompts, sample_len=12, temperature=0.8, seed=7, ignore_stop=True).tokens
+    b = lm.generate(prompts, sample_len=12, temperature=0.8, seed=7, ignore_stop=True).tokens
+    assert a == b and all(len(t) == 12 for t in a)          # the same draws from the same seed, through used slots
