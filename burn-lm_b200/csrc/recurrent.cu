@@ -10,10 +10,12 @@
 // A scan block owns (sequence, head, some value columns): 256 threads = columns x row groups; thread (col, rg) keeps rows
 // rg, rg + RG, rg + 2 RG, ... of its column in registers.  A sum over rows is a thread's partial sum and then shuffles
 // over the row groups (adjacent lanes): the same order whatever the step's size or batch.  RG = 8 (32 columns a block).
-// A warp a column (RG = 32, four times the warps, a quarter of the rows a thread) was measured and is slower: a 2,048-token
-// scan of 64 heads x 128 rows x 64 lanes 0.97 against 0.86 ms, 64 single tokens 0.117 against 0.067 ms: every block stages
-// the same B and C rows for a quarter of the columns.  The state is stored as [head][row / RG][column][row % RG], which is
-// the order in which a warp holds it.
+// More lanes a column were measured and left out.  RG = 32 (a warp a column, four times the warps): a 2,048-token scan of
+// 64 heads x 128 rows x 64 lanes 0.97 against 0.86 ms, 64 single tokens 0.117 against 0.067 ms.  RG = 16: that scan 0.86
+// against 0.79 ms (with the unrolled loop), the delta rule of 16 heads x 128 x 128 1.15 against 1.34 ms (its 64 blocks
+// become 128), single tokens 0.089 against 0.072 and 0.069 against 0.050 ms: every block stages the same rows of B and C
+// (or k, q and the decays) for fewer columns.  The state is stored as [head][row / RG][column][row % RG], which is the
+// order in which a warp holds it, so RG belongs to a model's state and cannot change from step to step.
 #include "common.cuh"
 
 BLM_API const char* blm_recurrent_last_error() { return g_blm_error; }
@@ -200,16 +202,20 @@ __global__ void __launch_bounds__(kScanThreads)
             decs[t] = expf(a * dt);
         }
         __syncthreads();
+        // (tokens unrolled: a token's shuffles and store wait for nothing the next token's multiply-adds need; the sum over
+        // a thread's rows in four partial sums, so that no chain of dependent additions is longer than RN / 4)
+#pragma unroll 4
         for (int t = 0; t < nt; ++t) {
             const float dec = decs[t], dt = dts[t], xv = xs[t * kCols + col];
             const float* b = Bs + t * NP + rg;
             const float* c = Cs + t * NP + rg;
-            float acc = 0.f;
+            float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int r = 0; r < RN; ++r) {
                 s[r] = dec * s[r] + (dt * b[r * kRowGroups]) * xv;
-                acc += s[r] * c[r * kRowGroups];
+                part[r & 3] += s[r] * c[r * kRowGroups];
             }
+            float acc = (part[0] + part[1]) + (part[2] + part[3]);
             acc = group_sum<RG>(acc);
             if (rg == 0 && live) y[(size_t)(sq.first + c0 + t) * y_stride + h * dv + col0 + col] = acc + skip * xv;
         }
@@ -286,25 +292,28 @@ __global__ void __launch_bounds__(kScanThreads)
             }
         }
         __syncthreads();
+#pragma unroll 2
         for (int t = 0; t < nt; ++t) {
             const float beta = betas[t], vv = vs[t * kCols + col];
             const float* kk = ks + t * NP + rg;
             const float* qq = qs + t * NP + rg;
             const float* gg = gs + t * NP + rg;
-            float acc = 0.f;
+            float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int r = 0; r < RN; ++r) {
                 s[r] *= gg[r * kRowGroups];
-                acc += s[r] * kk[r * kRowGroups];
+                part[r & 3] += s[r] * kk[r * kRowGroups];
             }
+            float acc = (part[0] + part[1]) + (part[2] + part[3]);
             acc = group_sum<RG>(acc);
             const float u = beta * (vv - acc);
-            float out = 0.f;
+            float outp[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int r = 0; r < RN; ++r) {
                 s[r] += kk[r * kRowGroups] * u;
-                out += s[r] * qq[r * kRowGroups];
+                outp[r & 3] += s[r] * qq[r * kRowGroups];
             }
+            float out = (outp[0] + outp[1]) + (outp[2] + outp[3]);
             out = group_sum<RG>(out);
             if (rg == 0 && live) o[(size_t)(sq.first + c0 + t) * o_stride + h * dv + col0 + col] = out;
         }
