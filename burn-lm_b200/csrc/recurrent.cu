@@ -20,7 +20,7 @@
 
 BLM_API const char* blm_recurrent_last_error() { return g_blm_error; }
 
-constexpr int kMaxTaps = 8;
+constexpr int kMaxTaps = 16;
 constexpr int kScanThreads = 256;
 constexpr int kChunk = 32;         // tokens staged in shared memory at a time
 
@@ -145,8 +145,8 @@ __device__ __forceinline__ ScanSeq scan_seq(int seq, const int* cu_seqlens, cons
     return s;
 }
 
-template <int RG>
-__device__ __forceinline__ float group_sum(float v) {       // over the row groups of a column (adjacent lanes)
+template <int RG, typename V>
+__device__ __forceinline__ V group_sum(V v) {       // over the row groups of a column (adjacent lanes)
 #pragma unroll
     for (int o = 1; o < RG; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
@@ -155,7 +155,10 @@ __device__ __forceinline__ float group_sum(float v) {       // over the row grou
 // State-space scan.  Per head h (group g = h / (heads / groups)), S [N x dv]:
 //     S <- exp(-exp(A_log_h) dt) S + dt B x^T;   y = S^T C + D_h x,    dt = softplus(dt_raw + dt_bias_h)
 // xbc [T, *]: x at x_col0 + h dv, B at b_col0 + g N, C at c_col0 + g N;  dt_raw [T, *] at dt_col0 + h.
-template <int RN, int RG>
+// AT: the type the state is held and summed in inside a step.  float: the serving path.  double: the 32-bit path, where a
+// head whose decay is close to 1 sums a thousand tokens into a state many times larger than its read-out (S^T C cancels),
+// and float sums alone put 1e-5 of the row's largest value on it; the carried state is rounded to float either way.
+template <int RN, int RG, typename AT>
 __global__ void __launch_bounds__(kScanThreads)
     ssm_scan_kernel(const float* __restrict__ xbc, long long xbc_stride, int x_col0, int b_col0, int c_col0,
                     const float* __restrict__ dt_raw, long long dt_stride, int dt_col0, const float* __restrict__ dt_bias,
@@ -164,12 +167,12 @@ __global__ void __launch_bounds__(kScanThreads)
                     const int* __restrict__ start_pos, float* __restrict__ state, long long slot_stride, long long copy_stride,
                     long long state_off) {
     constexpr int NP = RN * RG, kCols = kScanThreads / RG, kRowGroups = RG;
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     float* Bs = sm;                         // [kChunk][NP]
     float* Cs = Bs + kChunk * NP;           // [kChunk][NP]
     float* xs = Cs + kChunk * NP;           // [kChunk][kCols]
-    float* dts = xs + kChunk * kCols;       // [kChunk]
-    float* decs = dts + kChunk;             // [kChunk]
+    AT* dts = reinterpret_cast<AT*>(xs + kChunk * kCols);       // [kChunk]  (an even number of floats lies before it)
+    AT* decs = dts + kChunk;                                    // [kChunk]
     const int seq = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * kCols;
     const ScanSeq sq = scan_seq(seq, cu_seqlens, slot_of_seq, start_pos, state, slot_stride, copy_stride, state_off);
     if (sq.n_new <= 0) return;
@@ -177,10 +180,10 @@ __global__ void __launch_bounds__(kScanThreads)
     const int g = h / (heads / groups);
     const bool live = col0 + col < dv;
     const size_t head_off = (size_t)h * RN * dv * kRowGroups;
-    float s[RN];
+    AT s[RN];
 #pragma unroll
     for (int r = 0; r < RN; ++r)
-        s[r] = (sq.read && live) ? sq.read[head_off + ((size_t)r * dv + col0 + col) * kRowGroups + rg] : 0.f;
+        s[r] = (sq.read && live) ? (AT)sq.read[head_off + ((size_t)r * dv + col0 + col) * kRowGroups + rg] : (AT)0;
     const float a = -expf(A_log[h]);
     const float bias = dt_bias[h], skip = D[h];
     for (int c0 = 0; c0 < sq.n_new; c0 += kChunk) {
@@ -198,31 +201,32 @@ __global__ void __launch_bounds__(kScanThreads)
         }
         for (int t = tid; t < nt; t += blockDim.x) {
             const float dt = softplus_r(dt_raw[(size_t)(sq.first + c0 + t) * dt_stride + dt_col0 + h] + bias);
-            dts[t] = dt;
-            decs[t] = expf(a * dt);
+            dts[t] = (AT)dt;
+            if (sizeof(AT) == 8) decs[t] = (AT)exp((double)a * (double)dt);
+            else decs[t] = (AT)expf(a * dt);
         }
         __syncthreads();
         // (tokens unrolled: a token's shuffles and store wait for nothing the next token's multiply-adds need; the sum over
         // a thread's rows in four partial sums, so that no chain of dependent additions is longer than RN / 4)
 #pragma unroll 4
         for (int t = 0; t < nt; ++t) {
-            const float dec = decs[t], dt = dts[t], xv = xs[t * kCols + col];
+            const AT dec = decs[t], dt = dts[t], xv = (AT)xs[t * kCols + col];
             const float* b = Bs + t * NP + rg;
             const float* c = Cs + t * NP + rg;
-            float part[4] = {0.f, 0.f, 0.f, 0.f};
+            AT part[4] = {0, 0, 0, 0};
 #pragma unroll
             for (int r = 0; r < RN; ++r) {
-                s[r] = dec * s[r] + (dt * b[r * kRowGroups]) * xv;
-                part[r & 3] += s[r] * c[r * kRowGroups];
+                s[r] = dec * s[r] + (dt * (AT)b[r * kRowGroups]) * xv;
+                part[r & 3] += s[r] * (AT)c[r * kRowGroups];
             }
-            float acc = (part[0] + part[1]) + (part[2] + part[3]);
+            AT acc = (part[0] + part[1]) + (part[2] + part[3]);
             acc = group_sum<RG>(acc);
-            if (rg == 0 && live) y[(size_t)(sq.first + c0 + t) * y_stride + h * dv + col0 + col] = acc + skip * xv;
+            if (rg == 0 && live) y[(size_t)(sq.first + c0 + t) * y_stride + h * dv + col0 + col] = (float)(acc + (AT)skip * xv);
         }
     }
     if (live) {
 #pragma unroll
-        for (int r = 0; r < RN; ++r) sq.write[head_off + ((size_t)r * dv + col0 + col) * kRowGroups + rg] = s[r];
+        for (int r = 0; r < RN; ++r) sq.write[head_off + ((size_t)r * dv + col0 + col) * kRowGroups + rg] = (float)s[r];
     }
 }
 
@@ -240,7 +244,7 @@ __global__ void __launch_bounds__(kScanThreads)
                       const int* __restrict__ slot_of_seq, const int* __restrict__ start_pos, float* __restrict__ state,
                       long long slot_stride, long long copy_stride, long long state_off) {
     constexpr int NP = RN * RG, kCols = kScanThreads / RG, kRowGroups = RG;
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     float* ks = sm;                          // [kChunk][NP]
     float* qs = ks + kChunk * NP;            // [kChunk][NP]
     float* gs = qs + kChunk * NP;            // [kChunk][NP]
@@ -344,7 +348,7 @@ BLM_API int blm_ssm_scan(const float* xbc, long long xbc_stride, int x_col0, int
                          long long dt_stride, int dt_col0, const float* dt_bias, const float* A_log, const float* D, float* y,
                          long long y_stride, int heads, int groups, int N, int dv, const int* cu_seqlens, const int* slot_of_seq,
                          const int* start_pos, int n_seqs, float* state, long long slot_stride, long long copy_stride,
-                         long long state_off, cudaStream_t stream) {
+                         long long state_off, int wide_sums, cudaStream_t stream) {
     if (n_seqs == 0) return BLM_OK;
     const int rn = rows_per_thread(N);
     BLM_REQUIRE(rn > 0, "ssm_scan: a state of %d rows; this kernel takes up to %d", N, 32 * 8);
@@ -352,15 +356,22 @@ BLM_API int blm_ssm_scan(const float* xbc, long long xbc_stride, int x_col0, int
     BLM_REQUIRE(heads <= 65535 && dv <= 65535 * 8, "ssm_scan: too many heads");
     const int rg = row_groups(N), cols = kScanThreads / rg;
     dim3 grid(n_seqs, heads, (dv + cols - 1) / cols);
-    const size_t smem = ((size_t)2 * kChunk * rn * rg + kChunk * cols + 2 * kChunk) * sizeof(float);
+    const size_t smem = ((size_t)2 * kChunk * rn * rg + kChunk * cols) * sizeof(float) + 2 * kChunk * sizeof(double);
+#define SSM_ARGS xbc, xbc_stride, x_col0, b_col0, c_col0, dt_raw, dt_stride, dt_col0, dt_bias, A_log, D, y, y_stride, heads, groups, N, dv, cu_seqlens, slot_of_seq, start_pos, state, slot_stride, copy_stride, state_off
 #define BLM_SCAN(RN, RG)                                                                                 \
-    if (rn == RN && rg == RG) {                                                                          \
-        int rc = allow_smem(ssm_scan_kernel<RN, RG>, smem, "ssm_scan_kernel");                                   \
+    if (rn == RN && rg == RG && wide_sums) {                                                             \
+        int rc = allow_smem(ssm_scan_kernel<RN, RG, double>, smem, "ssm_scan_kernel");                   \
         if (rc != BLM_OK) return rc;                                                                     \
-        ssm_scan_kernel<RN, RG><<<grid, kScanThreads, smem, stream>>>(xbc, xbc_stride, x_col0, b_col0, c_col0, dt_raw, dt_stride, dt_col0, dt_bias, A_log, D, y, y_stride, heads, groups, N, dv, cu_seqlens, slot_of_seq, start_pos, state, slot_stride, copy_stride, state_off); \
+        ssm_scan_kernel<RN, RG, double><<<grid, kScanThreads, smem, stream>>>(SSM_ARGS);                 \
+    }                                                                                                    \
+    if (rn == RN && rg == RG && !wide_sums) {                                                            \
+        int rc = allow_smem(ssm_scan_kernel<RN, RG, float>, smem, "ssm_scan_kernel");                    \
+        if (rc != BLM_OK) return rc;                                                                     \
+        ssm_scan_kernel<RN, RG, float><<<grid, kScanThreads, smem, stream>>>(xbc, xbc_stride, x_col0, b_col0, c_col0, dt_raw, dt_stride, dt_col0, dt_bias, A_log, D, y, y_stride, heads, groups, N, dv, cu_seqlens, slot_of_seq, start_pos, state, slot_stride, copy_stride, state_off); \
     }
     BLM_SCAN(1, 8) BLM_SCAN(2, 8) BLM_SCAN(4, 8) BLM_SCAN(8, 8) BLM_SCAN(16, 8) BLM_SCAN(32, 8)
 #undef BLM_SCAN
+#undef SSM_ARGS
     return blm_check_launch("ssm_scan");
 }
 

@@ -110,7 +110,7 @@ _protos = {
                             c_int, c_void_p],
         "blm_ssm_scan": [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p,
                          c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                         c_longlong, c_longlong, c_longlong, c_void_p],
+                         c_longlong, c_longlong, c_longlong, c_int, c_void_p],
         "blm_delta_scan": [c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_int, c_void_p,
                            c_longlong, c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int,
                            c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_longlong, c_longlong,
@@ -1055,10 +1055,12 @@ def causal_conv(x, x_col0, channels, taps, bias, out, out_col0, step, state, sta
 
 
 def ssm_scan(xbc, x_col0, b_col0, c_col0, dt, dt_col0, dt_bias, a_log, d_skip, y, heads, groups, n_state, value_dim, step, state,
-             state_offset):
+             state_offset, wide_sums=False):
     """The state-space scan per head: S <- exp(-exp(A_log) dt) S + dt B x^T, y = S^T C + D x with dt = softplus(dt_raw +
     dt_bias); x [heads x value_dim], B and C [groups x n_state] are column ranges of xbc, dt_raw [heads] one of dt;
-    y float32 [N, heads * value_dim].  The state (fp32, carried per sequence) lies in `state` at state_offset."""
+    y float32 [N, heads * value_dim].  The state (fp32, carried per sequence) lies in `state` at state_offset.  `wide_sums`:
+    inside a step the state and the sums over its rows are held in float64 (the 32-bit path: a head that decays slowly sums
+    a long past into a state far larger than its read-out, whose cancellation float sums alone make visible)."""
     _need_cuda(dt_bias, a_log, d_skip, y, state)
     _f32(dt_bias, a_log, d_skip, y)
     xp, xs, xc = _cols(xbc, x_col0, heads * value_dim)
@@ -1069,7 +1071,7 @@ def ssm_scan(xbc, x_col0, b_col0, c_col0, dt, dt_col0, dt_bias, a_log, d_skip, y
         raise KernelError("ssm_scan: y float32 [N, heads * value_dim]")
     _call("recurrent", "blm_ssm_scan", xp, xs, xc, int(b_col0), int(c_col0), dp, ds, dc, _ptr(dt_bias), _ptr(a_log), _ptr(d_skip),
           _ptr(y), c_longlong(y.stride(0)), heads, groups, n_state, value_dim, _ptr(step.cu_seqlens), _ptr(step.slot_of_seq),
-          _ptr(step.start_pos), step.n_seqs, *_state_args(state, state_offset), _stream())
+          _ptr(step.start_pos), step.n_seqs, *_state_args(state, state_offset), 1 if wide_sums else 0, _stream())
 
 
 def delta_scan(q, q_col0, k, k_col0, v, v_col0, b, b_col0, a, a_col0, dt_bias, a_log, out, heads, qk_heads, key_dim, value_dim,

@@ -88,7 +88,7 @@ class Mamba2(Part):
         K.causal_conv(proj, inner, self.conv_channels, self.taps, self.conv_bias, xbc, 0, step, cache.state, 0, silu=True)
         y = torch.zeros((n, inner), dtype=torch.float32, device=proj.device)      # rows of no sequence stay zero
         K.ssm_scan(xbc, 0, inner, inner + gn, proj, 2 * inner + 2 * gn, self.dt_bias, self.a_log, self.d_skip, y,
-                   s.n_heads, s.groups, s.state, s.value_dim, step, cache.state, self.hist_floats)
+                   s.n_heads, s.groups, s.state, s.value_dim, step, cache.state, self.hist_floats, wide_sums=rt.exact)
         gated = torch.empty((n, inner), dtype=rt.dtype, device=proj.device)
         K.gated_group_norm(y, proj, 0, self.norm_weight, inner // s.norm_groups, K.GATE_FIRST, s.eps, gated)
         return self.o(gated, out_dtype=torch.float32)
