@@ -458,7 +458,7 @@ def nufolix_kernels(z, pk):
     out["attention_prefill_2048"] = {"llama_ms": round(ms_l, 4), "nufolix_ms": round(ms_n, 4), "mix_gflop_fp32": round(mix / 1e9, 1),
                                      "llama_frac_bf16": round(flops / (ms_l / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
                                      "nufolix_frac_bf16": round(flops / (ms_n / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
-    ms_l, ms_n, total = attention_case(64, 1, 1087, 4)
+    ms_l, ms_n, total = attention_case(64, 1, 1087, 4)         # the key ranges the mixer takes at this size
     nbytes = 64 * G * total * 2 * hd * 2
     out["attention_decode_b64"] = {"llama_ms": round(ms_l, 4), "nufolix_ms": round(ms_n, 4), "keys_seen": total,
                                    "llama_frac_hbm": round(nbytes / (ms_l / 1e3) / 1e9 / pk["hbm_gbs"], 4),

@@ -127,6 +127,22 @@ __device__ __forceinline__ float dot16(const __nv_bfloat16* a, const __nv_bfloat
     return acc;
 }
 
+// One row of `d` elements from global to shared memory, its lanes up to `dp` zeroed, by the lanes of a warp: in 16-byte
+// pieces when the row allows (d a multiple of a piece, both ends aligned), else element by element.  `live` false: zeros.
+template <typename T>
+__device__ __forceinline__ void stage_row(T* dst, const T* src, int d, int dp, bool live, int lane) {
+    constexpr int V = Vec<T>::n;
+    if (d % V == 0 && (((size_t)src | (size_t)dst) & 15) == 0) {
+        for (int c = lane; c < dp / V; c += 32) {
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (live && c < d / V) v = *reinterpret_cast<const uint4*>(src + c * V);
+            *reinterpret_cast<uint4*>(dst + c * V) = v;
+        }
+    } else {
+        for (int c = lane; c < dp; c += 32) dst[c] = (live && c < d) ? src[c] : from_f32<T>(0.f);
+    }
+}
+
 struct SigmoidAttnArgs {
     const void* q;            // [N, H dk]
     const void* pool;         // pages: keys [G][page][dk] then values [G][page][dv]
@@ -174,9 +190,10 @@ __global__ void __launch_bounds__(kThreads) sigmoid_attn_kernel(const SigmoidAtt
     for (int e = tid; e < H; e += kThreads) pbs[e] = a.head_bias ? a.head_bias[e] : 0.f;
     // the tile's queries, rows beyond the tile and lanes beyond dk as zeros
     const T* q = reinterpret_cast<const T*>(a.q);
-    for (int e = tid; e < H * BQ * dkp; e += kThreads) {
-        const int l = e % dkp, i = (e / dkp) % BQ, h = e / (dkp * BQ);
-        Qs[e] = (l < dk && i < nq) ? q[(size_t)(first + i0 + i) * H * dk + h * dk + l] : from_f32<T>(0.f);
+    const int lane = tid & 31, warp = tid >> 5;
+    for (int r = warp; r < H * BQ; r += kThreads / 32) {           // a warp a row
+        const int i = r % BQ, h = r / BQ;
+        stage_row(Qs + (size_t)r * dkp, q + (size_t)(first + i0 + i) * H * dk + h * dk, dk, dkp, i < nq, lane);
     }
     float acc[ACC];
 #pragma unroll
@@ -192,9 +209,9 @@ __global__ void __launch_bounds__(kThreads) sigmoid_attn_kernel(const SigmoidAtt
         const T* pg = pool + (size_t)table[j0 / a.page] * page_elems;
         const int at0 = j0 % a.page;
         __syncthreads();                                  // the chunk before is done with KVs, Ss and Ms
-        for (int e = tid; e < G * KC * dkp; e += kThreads) {
-            const int l = e % dkp, j = (e / dkp) % KC, g = e / (dkp * KC);
-            KVs[e] = (l < dk && j0 + j < kv_hi) ? pg[((size_t)g * a.page + at0 + j) * dk + l] : from_f32<T>(0.f);
+        for (int r = warp; r < G * KC; r += kThreads / 32) {
+            const int j = r % KC, g = r / KC;
+            stage_row(KVs + (size_t)r * dkp, pg + ((size_t)g * a.page + at0 + j) * dk, dk, dkp, j0 + j < kv_hi, lane);
         }
         __syncthreads();
         // scores and weights of all heads
@@ -210,10 +227,9 @@ __global__ void __launch_bounds__(kThreads) sigmoid_attn_kernel(const SigmoidAtt
         }
         __syncthreads();
         // the values take the keys' place while the weights are mixed
-        for (int e = tid; e < G * KC * dvp; e += kThreads) {
-            const int l = e % dvp, j = (e / dvp) % KC, g = e / (dvp * KC);
-            KVs[e] = (l < dv && j0 + j < kv_hi)
-                         ? pg[(size_t)G * a.page * dk + ((size_t)g * a.page + at0 + j) * dv + l] : from_f32<T>(0.f);
+        for (int r = warp; r < G * KC; r += kThreads / 32) {
+            const int j = r % KC, g = r / KC;
+            stage_row(KVs + (size_t)r * dvp, pg + (size_t)G * a.page * dk + ((size_t)g * a.page + at0 + j) * dv, dv, dvp, j0 + j < kv_hi, lane);
         }
         const int ij = BQ * KC;
         for (int e = tid; e < H * ij; e += kThreads) {
@@ -276,6 +292,7 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const unsigned (&a)[4],
 }
 
 constexpr int kRows = 16;          // query rows of a block of the tensor-core kernel
+constexpr int kMmaMinRows = 2;      // single tokens run the CUDA-core kernel (see the measurements beside launch_sigmoid_attention_mma)
 constexpr int kThreadsMma = 512;   // sixteen warps: the weights' exponentials and the mix want many warps in flight
 
 struct MmaLayout {                 // strides and offsets (bytes) of the block's shared memory
@@ -521,11 +538,15 @@ static bool plan_for(int H, int G, int dk, int dv, int max_q_len, int page, Sigm
     int BQ = 8;
     while (BQ > 1 && ((size_t)H * BQ * dv > (size_t)64 * kThreads || BQ / 2 >= max_q_len)) BQ /= 2;
     if ((size_t)H * BQ * dv > (size_t)64 * kThreads) return false;
-    for (; BQ >= 1; BQ /= 2) {
+    // single rows (decoding) are bound by the latency of their loads: a chunk small enough for four blocks an SM, if any
+    const size_t roomy = max_q_len == 1 ? 56 * 1024 : limit;
+    for (int pass = 0; pass < 2; ++pass)
+    for (int bq = BQ; bq >= 1; bq /= 2) {
         for (int KC = 64; KC >= 16; KC /= 2) {
             if (KC > page || page % KC) continue;
-            const size_t s = smem_bytes<T>(H, G, dk, dv, BQ, KC);
-            if (s <= limit) {
+            const size_t s = smem_bytes<T>(H, G, dk, dv, bq, KC);
+            if (s <= (pass == 0 ? roomy : limit)) {
+                BQ = bq;
                 const size_t outs = ((size_t)H * BQ * dv + kThreads - 1) / kThreads;
                 p->BQ = BQ;
                 p->KC = KC;
@@ -551,7 +572,7 @@ static int finish_ranges_bf16(const SigmoidAttnArgs& a, const int* token_seq, cu
 static int launch_sigmoid_attention_mma(SigmoidAttnArgs a, int max_q_len, const int* token_seq, cudaStream_t stream) {
     int KC, HG, NT;
     size_t smem;
-    if (!mma_plan(a.H, a.G, a.dk, a.dv, a.page, &KC, &HG, &NT, &smem)) return -1;
+    if (max_q_len < kMmaMinRows || !mma_plan(a.H, a.G, a.dk, a.dv, a.page, &KC, &HG, &NT, &smem)) return -1;
     if ((((size_t)a.q | (size_t)a.pool | (size_t)a.out) & 15) != 0) return -1;
     a.BQ = kRows;
     a.KC = KC;

@@ -95,8 +95,9 @@ class SigmoidAttention(Part):
         """Over how many blocks a query's keys are cut: nothing is normalised over the keys, so partial outputs just add.
         Few query rows with long pasts (decoding) would leave most multiprocessors idle otherwise."""
         tiles = step.n_seqs * ((step.max_q_len + 15) // 16)
-        want = BLOCKS_PER_SM * K.sm_count(self.runtime.device)
-        return max(1, min((want + tiles - 1) // tiles, step.max_kv_len // RANGE_KEYS, 64))
+        want = (4 if step.max_q_len == 1 else BLOCKS_PER_SM) * K.sm_count(self.runtime.device)      # single rows: small blocks, four an SM
+        shortest = K.PAGE if step.max_q_len == 1 else RANGE_KEYS                  # a single row's range may be one page
+        return max(1, min((want + tiles - 1) // tiles, step.max_kv_len // shortest, 64))
 
     def forward(self, x, step, cache):
         s, rt = self.spec, self.runtime
