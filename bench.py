@@ -432,8 +432,11 @@ def nufolix_kernels(z, pk):
                                cu_seqlens=i32([new * s for s in range(n_seqs + 1)]), start_pos=i32([cached] * n_seqs),
                                n_tokens=n_seqs * new, n_seqs=n_seqs, max_q_len=new, max_kv_len=cached + new)
 
-    def attention_case(n_seqs, new, cached, ranges):
+    def attention_case(n_seqs, new, cached):
         total = cached + new
+        # the key ranges the mixer takes at this size (parts.sigmoid_attention.SigmoidAttention._ranges)
+        tiles, sms = n_seqs * (-(-new // 16)), K.sm_count()
+        ranges = max(1, min(-(-(4 if new == 1 else 2) * sms // tiles), total // (K.PAGE if new == 1 else 256), 64))
         pages_each = -(-total // K.PAGE)
         n = n_seqs * new
         bt = torch.arange(n_seqs * pages_each, dtype=torch.int32, device=dev).reshape(n_seqs, pages_each)
@@ -449,18 +452,18 @@ def nufolix_kernels(z, pk):
         partial = torch.empty(ranges * n * H * hd, dtype=torch.float32, device=dev) if ranges > 1 else None
         ms_new = _time(lambda: K.sigmoid_attention(q, pool, bt, st, o, H, G, hd, hd, hd ** -0.5, softcap=30.0, talk=talk, head_bias=pb,
                                                    ranges=ranges, partial=partial), reps=3)
-        return ms_llama, ms_new, total
+        return ms_llama, ms_new, total, ranges
 
-    ms_l, ms_n, total = attention_case(1, 2048, 0, 3)          # the key ranges the mixer takes at this size
+    ms_l, ms_n, total, ranges = attention_case(1, 2048, 0)
     pairs = 2048 * 2049 / 2
     flops = 4.0 * H * hd * pairs
     mix = 2.0 * H * H * pairs                      # the heads' mix: fp32 multiply-adds outside the tensor cores
-    out["attention_prefill_2048"] = {"llama_ms": round(ms_l, 4), "nufolix_ms": round(ms_n, 4), "mix_gflop_fp32": round(mix / 1e9, 1),
+    out["attention_prefill_2048"] = {"llama_ms": round(ms_l, 4), "nufolix_ms": round(ms_n, 4), "key_ranges": ranges, "mix_gflop_fp32": round(mix / 1e9, 1),
                                      "llama_frac_bf16": round(flops / (ms_l / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
                                      "nufolix_frac_bf16": round(flops / (ms_n / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
-    ms_l, ms_n, total = attention_case(64, 1, 1087, 4)         # the key ranges the mixer takes at this size
+    ms_l, ms_n, total, ranges = attention_case(64, 1, 1087)
     nbytes = 64 * G * total * 2 * hd * 2
-    out["attention_decode_b64"] = {"llama_ms": round(ms_l, 4), "nufolix_ms": round(ms_n, 4), "keys_seen": total,
+    out["attention_decode_b64"] = {"llama_ms": round(ms_l, 4), "nufolix_ms": round(ms_n, 4), "keys_seen": total, "key_ranges": ranges,
                                    "llama_frac_hbm": round(nbytes / (ms_l / 1e3) / 1e9 / pk["hbm_gbs"], 4),
                                    "nufolix_frac_hbm": round(nbytes / (ms_n / 1e3) / 1e9 / pk["hbm_gbs"], 4)}
     # the scans: prompts read and write rows (a pass over their inputs and outputs), single tokens the states

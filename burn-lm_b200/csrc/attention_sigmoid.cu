@@ -292,7 +292,7 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const unsigned (&a)[4],
 }
 
 constexpr int kRows = 16;          // query rows of a block of the tensor-core kernel
-constexpr int kMmaMinRows = 2;      // single tokens run the CUDA-core kernel (see the measurements beside launch_sigmoid_attention_mma)
+constexpr int kMmaMinRows = 2;      // steps whose longest run is one token run the kernel whose rows are heads, or the CUDA-core kernel
 constexpr int kThreadsMma = 512;   // sixteen warps: the weights' exponentials and the mix want many warps in flight
 
 struct MmaLayout {                 // strides and offsets (bytes) of the block's shared memory
@@ -481,6 +481,211 @@ __global__ void __launch_bounds__(kThreadsMma) sigmoid_attn_mma_kernel(const Sig
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Single tokens on the tensor cores (bfloat16): one query a sequence, so the rows of a tile are the HEADS of a key/value
+// head (up to 16), as in the dense decoder's decode kernel.  A block owns (sequence, range of keys) with all heads: per
+// chunk of keys one score tile per key/value head, the weights of all heads in fp32, the mix, one value product per
+// key/value head.  No head groups: a block's outputs are heads x value lanes.
+// ---------------------------------------------------------------------------------------------
+struct RowsLayout {
+    int dkp, dvp, kvp, ssp, msp, hpad;
+    size_t ts, pbs, ss, ms, qs, kv, total;
+};
+
+__host__ __device__ inline RowsLayout rows_layout(int H, int G, int dk, int dv, int KC) {
+    RowsLayout l;
+    l.dkp = dk + 8;
+    l.dvp = dv + 8;
+    l.kvp = l.dkp > l.dvp ? l.dkp : l.dvp;
+    l.ssp = KC;
+    l.msp = KC + 8;
+    l.hpad = (H + 7) / 8 * 8;
+    l.ts = 0;                                               // [H][hpad] floats: talk transposed
+    l.pbs = l.ts + (size_t)H * l.hpad * 4;                  // [H] floats
+    l.ss = l.pbs + (size_t)((H + 3) / 4 * 4) * 4;           // [H][ssp] floats: the one query's weights
+    l.ms = l.ss + (size_t)H * l.ssp * 4;                    // [G][16][msp] bfloat16: mixed weights, a head a row
+    l.qs = l.ms + (size_t)G * kRows * l.msp * 2;            // [G][16][dkp] bfloat16: the query, a head a row
+    l.kv = l.qs + (size_t)G * kRows * l.dkp * 2;            // [G][KC][kvp] bfloat16
+    l.total = l.kv + (size_t)G * KC * l.kvp * 2;
+    return l;
+}
+
+template <int NT>
+__global__ void __launch_bounds__(kThreads) sigmoid_attn_rows_kernel(const SigmoidAttnArgs a) {
+    typedef __nv_bfloat16 T;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int H = a.H, G = a.G, dk = a.dk, dv = a.dv, KC = a.KC;
+    const RowsLayout L = rows_layout(H, G, dk, dv, KC);
+    float* Ts = reinterpret_cast<float*>(smem_raw + L.ts);
+    float* pbs = reinterpret_cast<float*>(smem_raw + L.pbs);
+    float* Ss = reinterpret_cast<float*>(smem_raw + L.ss);
+    T* Ms = reinterpret_cast<T*>(smem_raw + L.ms);
+    T* Qs = reinterpret_cast<T*>(smem_raw + L.qs);
+    T* KVs = reinterpret_cast<T*>(smem_raw + L.kv);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int seq = blockIdx.x;
+    const int first = a.cu_seqlens[seq];
+    if (a.cu_seqlens[seq + 1] - first != 1) return;      // this kernel serves sequences that bring one token
+    const int kv_hi = a.start_pos[seq] + 1;
+    const int chunks = (kv_hi + KC - 1) / KC;
+    const int per = (chunks + a.ranges - 1) / a.ranges;
+    const int c_lo = blockIdx.y * per, c_hi = min(chunks, c_lo + per);
+    const int* table = a.block_table + (size_t)a.slot_of_seq[seq] * a.table_stride;
+    const int per_kv = H / G;
+    const int HD = H * dv;
+    const int dk8 = dk / 8, dv8 = dv / 8;
+    const int own_tiles = G * dv8;
+
+    for (int e = tid; e < H * L.hpad; e += kThreads) {
+        const int g = e / L.hpad, h = e % L.hpad;
+        Ts[e] = h < H ? (a.talk ? a.talk[(size_t)h * H + g] : (h == g ? 1.f : 0.f)) : 0.f;
+    }
+    for (int e = tid; e < H; e += kThreads) pbs[e] = a.head_bias ? a.head_bias[e] : 0.f;
+    for (int e = tid; e < G * kRows * L.msp / 8; e += kThreads) reinterpret_cast<uint4*>(Ms)[e] = make_uint4(0, 0, 0, 0);
+    const T* q = reinterpret_cast<const T*>(a.q) + (size_t)first * H * dk;
+    for (int e = tid; e < G * kRows * dk8; e += kThreads) {
+        const int c = e % dk8, r = (e / dk8) % kRows, g = e / (dk8 * kRows);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < per_kv) v = *reinterpret_cast<const uint4*>(q + (size_t)(g * per_kv + r) * dk + c * 8);
+        *reinterpret_cast<uint4*>(Qs + (size_t)(g * kRows + r) * L.dkp + c * 8) = v;
+    }
+    float acc[NT][4];
+#pragma unroll
+    for (int x = 0; x < NT; ++x) acc[x][0] = acc[x][1] = acc[x][2] = acc[x][3] = 0.f;
+    const T* pool = reinterpret_cast<const T*>(a.pool);
+    const size_t page_elems = (size_t)G * a.page * (dk + dv);
+    const bool cap = a.softcap > 0.f;
+    const float inv_cap = cap ? 1.0f / a.softcap : 0.f;
+    const int kc8 = KC / 8;
+
+    for (int ch = c_lo; ch < c_hi; ++ch) {
+        const int j0 = ch * KC;
+        const T* pg = pool + (size_t)table[j0 / a.page] * page_elems;
+        const int at0 = j0 % a.page;
+        __syncthreads();
+        for (int e = tid; e < G * KC * dk8; e += kThreads) {
+            const int c = e % dk8, j = (e / dk8) % KC, g = e / (dk8 * KC);
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (j0 + j < kv_hi) v = *reinterpret_cast<const uint4*>(pg + ((size_t)g * a.page + at0 + j) * dk + c * 8);
+            *reinterpret_cast<uint4*>(KVs + (size_t)(g * KC + j) * L.dkp + c * 8) = v;
+        }
+        __syncthreads();
+        for (int s = warp; s < G * kc8; s += kThreads / 32) {           // a score tile: the heads of a kv head x 8 keys
+            const int g = s / kc8, nt = s % kc8;
+            float c4[4] = {0.f, 0.f, 0.f, 0.f};
+            const T* qa = Qs + (size_t)(g * kRows + (lane & 15)) * L.dkp + (lane >> 4) * 8;
+            const T* kb = KVs + (size_t)(g * KC + nt * 8 + (lane & 7)) * L.dkp + ((lane >> 3) & 1) * 8;
+            for (int kk = 0; kk < dk; kk += 16) {
+                unsigned af[4], bf[2];
+                ldsm_x4(af, qa + kk);
+                ldsm_x2(bf, kb + kk);
+                mma_16816(c4, af, bf);
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const int row = (lane >> 2) + 8 * r;
+                if (row < per_kv) {
+                    const int h = g * per_kv + row;
+                    float w2[2];
+#pragma unroll
+                    for (int cc = 0; cc < 2; ++cc) {
+                        const int j = nt * 8 + 2 * (lane & 3) + cc;
+                        float w = 0.f;
+                        if (j0 + j < kv_hi) {
+                            float sc = c4[2 * r + cc] * a.scale;
+                            if (cap) sc = a.softcap * (1.0f - __fdividef(2.0f, 1.0f + __expf(2.0f * sc * inv_cap)));
+                            w = __fdividef(1.0f, 1.0f + __expf(-(sc + pbs[h])));
+                        }
+                        w2[cc] = w;
+                    }
+                    *reinterpret_cast<float2*>(Ss + (size_t)h * L.ssp + nt * 8 + 2 * (lane & 3)) = make_float2(w2[0], w2[1]);
+                }
+            }
+        }
+        __syncthreads();
+        for (int e = tid; e < G * KC * dv8; e += kThreads) {
+            const int c = e % dv8, j = (e / dv8) % KC, g = e / (dv8 * KC);
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (j0 + j < kv_hi) v = *reinterpret_cast<const uint4*>(pg + (size_t)G * a.page * dk + ((size_t)g * a.page + at0 + j) * dv + c * 8);
+            *reinterpret_cast<uint4*>(KVs + (size_t)(g * KC + j) * L.dvp + c * 8) = v;
+        }
+        for (int e = tid; e < (L.hpad / 8) * KC; e += kThreads) {         // the mix: eight heads a thread at one key
+            const int j = e % KC, hc = e / KC;
+            float m[8];
+#pragma unroll
+            for (int x = 0; x < 8; ++x) m[x] = 0.f;
+            const float* tp = Ts + hc * 8;
+            for (int g = 0; g < H; ++g) {
+                const float sv = Ss[(size_t)g * L.ssp + j];
+                const float4 t0 = *reinterpret_cast<const float4*>(tp + (size_t)g * L.hpad);
+                const float4 t1 = *reinterpret_cast<const float4*>(tp + (size_t)g * L.hpad + 4);
+                m[0] += t0.x * sv; m[1] += t0.y * sv; m[2] += t0.z * sv; m[3] += t0.w * sv;
+                m[4] += t1.x * sv; m[5] += t1.y * sv; m[6] += t1.z * sv; m[7] += t1.w * sv;
+            }
+#pragma unroll
+            for (int x = 0; x < 8; ++x) {
+                const int h = hc * 8 + x;
+                if (h < H) Ms[(size_t)((h / per_kv) * kRows + h % per_kv) * L.msp + j] = __float2bfloat16_rn(m[x]);
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int x = 0; x < NT; ++x) {
+            const int t = warp * NT + x;
+            if (t < own_tiles) {
+                const int g = t / dv8, nt = t % dv8;
+                const T* ma = Ms + (size_t)(g * kRows + (lane & 15)) * L.msp + (lane >> 4) * 8;
+                const T* vb = KVs + (size_t)(g * KC + (lane & 15)) * L.dvp + nt * 8;
+                for (int kk = 0; kk < KC; kk += 16) {
+                    unsigned af[4], bf[2];
+                    ldsm_x4(af, ma + kk);
+                    ldsm_x2_trans(bf, vb + (size_t)kk * L.dvp);
+                    mma_16816(acc[x], af, bf);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int x = 0; x < NT; ++x) {
+        const int t = warp * NT + x;
+        if (t < own_tiles) {
+            const int g = t / dv8, nt = t % dv8;
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const int row = (lane >> 2) + 8 * r;
+                if (row < per_kv) {
+                    const size_t at = (size_t)first * HD + (size_t)(g * per_kv + row) * dv + nt * 8 + 2 * (lane & 3);
+                    if (a.ranges > 1) {
+                        *reinterpret_cast<float2*>(a.partial + (size_t)blockIdx.y * a.n_tokens * HD + at) = make_float2(acc[x][2 * r], acc[x][2 * r + 1]);
+                    } else {
+                        *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<T*>(a.out) + at) = __floats2bfloat162_rn(acc[x][2 * r], acc[x][2 * r + 1]);
+                    }
+                }
+            }
+        }
+    }
+}
+
+// (KC, NT) of the single-token tensor-core kernel for a shape, or false when it does not take it
+static bool rows_plan(int H, int G, int dk, int dv, int page, int* KC_out, int* NT_out, size_t* smem_out) {
+    if (dk % 16 || dv % 8 || H % G || H / G > kRows) return false;
+    const int nt = (G * (dv / 8) + kThreads / 32 - 1) / (kThreads / 32);
+    if (nt > 16) return false;
+    const size_t room[3] = {72 * 1024, 110 * 1024, 200 * 1024};      // three blocks an SM if a chunk allows, else two, else one
+    for (int pass = 0; pass < 3; ++pass)
+        for (int KC = 32; KC >= 16; KC /= 2) {
+            if (page % KC) continue;
+            const RowsLayout l = rows_layout(H, G, dk, dv, KC);
+            if (l.total <= room[pass]) {
+                *KC_out = KC;
+                *NT_out = nt <= 2 ? 2 : (nt <= 4 ? 4 : (nt <= 8 ? 8 : 16));
+                *smem_out = l.total;
+                return true;
+            }
+        }
+    return false;
+}
+
 // (KC, HG, NT) of the tensor-core kernel for a shape, or false when it does not take it
 static bool mma_plan(int H, int G, int dk, int dv, int page, int* KC_out, int* HG_out, int* NT_out, size_t* smem_out) {
     if (dk % 16 || dv % 8 || H % G) return false;
@@ -572,8 +777,30 @@ static int finish_ranges_bf16(const SigmoidAttnArgs& a, const int* token_seq, cu
 static int launch_sigmoid_attention_mma(SigmoidAttnArgs a, int max_q_len, const int* token_seq, cudaStream_t stream) {
     int KC, HG, NT;
     size_t smem;
-    if (max_q_len < kMmaMinRows || !mma_plan(a.H, a.G, a.dk, a.dv, a.page, &KC, &HG, &NT, &smem)) return -1;
     if ((((size_t)a.q | (size_t)a.pool | (size_t)a.out) & 15) != 0) return -1;
+    if (max_q_len == 1) {            // single tokens: the heads of a key/value head are a tile's rows
+        if (!rows_plan(a.H, a.G, a.dk, a.dv, a.page, &KC, &NT, &smem)) return -1;
+        a.BQ = 1;
+        a.KC = KC;
+        a.q_tiles = 1;
+        BLM_REQUIRE(a.ranges <= 65535, "sigmoid_attention: grid too large");
+        dim3 grid(a.n_seqs, a.ranges);
+#define BLM_SAR(N)                                                                                                       \
+    {                                                                                                                    \
+        auto k = sigmoid_attn_rows_kernel<N>;                                                                            \
+        if (smem > 48 * 1024) {                                                                                          \
+            cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);             \
+            if (e != cudaSuccess) return blm_fail(BLM_CUDA_ERROR, "sigmoid_attention: %s", cudaGetErrorString(e));       \
+        }                                                                                                                \
+        k<<<grid, kThreads, smem, stream>>>(a);                                                                          \
+    }
+        if (NT == 2) BLM_SAR(2) else if (NT == 4) BLM_SAR(4) else if (NT == 8) BLM_SAR(8) else BLM_SAR(16)
+#undef BLM_SAR
+        int rc = blm_check_launch("sigmoid_attention (single tokens, tensor cores)");
+        if (rc != BLM_OK || a.ranges == 1) return rc;
+        return finish_ranges_bf16(a, token_seq, stream);
+    }
+    if (max_q_len < kMmaMinRows || !mma_plan(a.H, a.G, a.dk, a.dv, a.page, &KC, &HG, &NT, &smem)) return -1;
     a.BQ = kRows;
     a.KC = KC;
     a.q_tiles = (max_q_len + kRows - 1) / kRows;
