@@ -15,7 +15,9 @@
 // against 0.79 ms (with the unrolled loop), the delta rule of 16 heads x 128 x 128 1.15 against 1.34 ms (its 64 blocks
 // become 128), single tokens 0.089 against 0.072 and 0.069 against 0.050 ms: every block stages the same rows of B and C
 // (or k, q and the decays) for fewer columns.  The state is stored as [head][row / RG][column][row % RG], which is the
-// order in which a warp holds it, so RG belongs to a model's state and cannot change from step to step.
+// order in which a warp holds it, so RG belongs to a model's state and cannot change from step to step.  Fewer columns a
+// block (16, in blocks of 128 threads, where a single sequence's 64 blocks would become 128) made the delta rule's prompt
+// scan slower as well, 1.86 against 1.38 ms: the staging of a chunk is shared by fewer threads.
 #include "common.cuh"
 
 BLM_API const char* blm_recurrent_last_error() { return g_blm_error; }
