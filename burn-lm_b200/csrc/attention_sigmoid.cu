@@ -75,7 +75,7 @@ BLM_API int blm_bias_rope_append(const float* proj, long long stride, const floa
     if (n == 0) return BLM_OK;
     BLM_REQUIRE(H > 0 && G > 0 && dk > 0 && dv > 0 && page > 0, "bias_rope_append: bad sizes");
     BLM_REQUIRE(rot >= 0 && rot <= dk && rot % 2 == 0 && (rot == 0 || freq != nullptr), "bias_rope_append: %d rotated lanes of %d", rot, dk);
-    BLM_REQUIRE(n <= 65535 * 64, "bias_rope_append: too many rows");
+    BLM_REQUIRE(n <= 65535, "bias_rope_append: a step of %d rows; this kernel takes 65,535", n);
     const int width = (H + G) * dk + G * dv;
     dim3 grid((width + 255) / 256, n);
     if (dtype == BLM_F32)
@@ -866,7 +866,7 @@ BLM_API int blm_sigmoid_attention(const void* q, const void* pool, int dtype, co
     if (n_tokens == 0 || n_seqs == 0) return BLM_OK;
     BLM_REQUIRE(H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0 && max_q_len > 0, "sigmoid_attention: bad sizes");
     BLM_REQUIRE(ranges >= 1 && (ranges == 1 || partial != nullptr), "sigmoid_attention: several key ranges need a workspace");
-    BLM_REQUIRE(n_tokens <= 65535 * 64, "sigmoid_attention: too many rows");
+    BLM_REQUIRE(n_tokens <= 65535, "sigmoid_attention: a step of %d rows; this kernel takes 65,535", n_tokens);
     SigmoidAttnArgs a;
     a.q = q; a.pool = pool; a.block_table = block_table; a.table_stride = table_stride; a.cu_seqlens = cu_seqlens;
     a.slot_of_seq = slot_of_seq; a.start_pos = start_pos; a.talk = talk; a.head_bias = head_bias; a.out = out; a.partial = partial;

@@ -112,7 +112,7 @@ BLM_API int blm_causal_conv(const float* x, long long x_stride, int x_col0, int 
                             int single_tokens, cudaStream_t stream) {
     if (n_tokens == 0) return BLM_OK;
     BLM_REQUIRE(channels > 0 && K >= 1 && K <= kMaxTaps, "causal_conv: %d taps; this kernel takes 1 to %d", K, kMaxTaps);
-    BLM_REQUIRE(n_tokens <= 65535 * 64 && n_seqs <= 65535, "causal_conv: too many rows");
+    BLM_REQUIRE(n_tokens <= 65535 && n_seqs <= 65535, "causal_conv: a step of %d rows; this kernel takes 65,535", n_tokens);
     const int threads = 128;
     dim3 grid((channels + threads - 1) / threads, n_tokens);
     conv_kernel<<<grid, threads, 0, stream>>>(x, x_stride, x_col0, channels, taps, bias, K, act, out, out_stride, out_col0,

@@ -122,17 +122,18 @@ __device__ __forceinline__ float softplus_f(float v) { return fmaxf(v, 0.f) + lo
 
 template <typename TI, typename TA>
 __global__ void bias_act_kernel(const TI* __restrict__ x, const float* __restrict__ bias, const float* __restrict__ params,
-                                TA* __restrict__ out, size_t total, int width, int kind) {
+                                TA* __restrict__ out, int width, int kind) {
     float ap = 0.f, an = 0.f;
     if (kind == 1) {
         ap = softplus_f(params[0]);
         an = 0.5f + softplus_f(params[1]);
     }
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        float z = to_f32(x[i]);
-        if (bias) z += bias[i % width];
+    const size_t row = (size_t)blockIdx.y * width;       // a row a blockIdx.y: no division to find an element's bias
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < width; c += gridDim.x * blockDim.x) {
+        float z = to_f32(x[row + c]);
+        if (bias) z += bias[c];
         if (kind == 1) z = z > 0.f ? ap * z * z + 0.5f * z : an * (expm1f(z) - z) + 0.5f * z;
-        out[i] = from_f32<TA>(z);
+        out[row + c] = from_f32<TA>(z);
     }
 }
 
@@ -141,10 +142,10 @@ BLM_API int blm_bias_act(const void* x, int x_dtype, const float* bias, const fl
     if (n == 0) return BLM_OK;
     BLM_REQUIRE(n > 0 && width > 0 && (kind == 0 || kind == 1), "bias_act: bad sizes or kind");
     BLM_REQUIRE(kind == 0 || params != nullptr, "bias_act: the activation needs its two numbers");
-    const size_t total = (size_t)n * width;
+    BLM_REQUIRE(n <= 65535, "bias_act: %d rows; this kernel takes 65,535", n);
     const int threads = 256;
-    const int blocks = (int)((total + threads - 1) / threads < 65535u * 16u ? (total + threads - 1) / threads : 65535u * 16u);
-#define BLM_BA(TI, TA) bias_act_kernel<TI, TA><<<blocks, threads, 0, stream>>>((const TI*)x, bias, params, (TA*)out, total, width, kind)
+    dim3 grid((width + threads - 1) / threads < 64 ? (width + threads - 1) / threads : 64, n);
+#define BLM_BA(TI, TA) bias_act_kernel<TI, TA><<<grid, threads, 0, stream>>>((const TI*)x, bias, params, (TA*)out, width, kind)
     if (x_dtype == BLM_F32 && out_dtype == BLM_F32) BLM_BA(float, float);
     else if (x_dtype == BLM_F32 && out_dtype == BLM_BF16) BLM_BA(float, __nv_bfloat16);
     else if (x_dtype == BLM_BF16 && out_dtype == BLM_BF16) BLM_BA(__nv_bfloat16, __nv_bfloat16);
