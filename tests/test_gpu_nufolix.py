@@ -594,3 +594,23 @@ def test_a_slowly_decaying_head_keeps_its_long_past_in_the_32_bit_path():
         at += portion
     err = np.abs(np.concatenate(outs) - want).max(axis=1) / np.abs(want).max(axis=1)
     assert err.max() < 2e-6, err.max()
+
+
+@pytest.mark.parametrize("kinds", ["mamba2 only", "parallel only", "mamba2 last"])
+def test_models_of_one_kind_of_layer(tmp_path, kinds):
+    """No keys and values at all, no recurrent layer of the first kind at all, and another order of layers."""
+    from burn_lm_b200 import write_random_model
+    from nufolix_tiny import mamba2, model, parallel
+    layers = {"mamba2 only": [mamba2(2, 16, 8, 1, 3, 1, 40), mamba2(4, 8, 16, 2, 2, 2, None)],
+              "parallel only": [parallel(2, 1, 16, 8, 8, 2, 2, 8, 16, 2, None), parallel(3, 3, 8, 16, 0, 1, 1, 16, 8, 3, 24)],
+              "mamba2 last": [parallel(2, 2, 16, 16, 16, 2, 1, 16, 16, 4, 32), parallel(4, 2, 8, 8, 4, 4, 4, 8, 8, 2, None),
+                              mamba2(3, 8, 8, 3, 4, 3, None)]}[kinds]
+    cfg = model(97, 48, layers)
+    folder = write_random_model(str(tmp_path / "m"), cfg, seed=3, dtype="bfloat16")
+    pcfg, tensors = P.read_model_folder(folder)
+    tokens = random_tokens(7, 90, 97)
+    want = P.forward(pcfg, tensors, tokens)
+    for dtype, tol in (("float32", FP32_TOL), ("bfloat16", BF16_TOL)):
+        engine = engine_for(folder, dtype)
+        assert row_error(_logits(engine, tokens, list(range(90)), [70] + [1] * 20), want).max() < tol
+        assert row_error(_logits(engine, tokens, list(range(90)), [3, 64, 2, 21]), want).max() < tol
